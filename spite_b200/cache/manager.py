@@ -64,6 +64,18 @@ class Window:
         """Lowest position visible to the token at `pos` (the kernels use the same rule)."""
         return self.first_needed(pos)
 
+    def union(self, other: "Window") -> "Window":
+        """A window that keeps whatever either of the two still reads: the rule by which a cache that layers with
+        different windows share gives its pages back.  Equal windows: that window; two chunk sizes of which one
+        divides the other: the larger; two sliding windows: the longer; anything else keeps every key."""
+        if self == other:
+            return self
+        if self.kind == other.kind == "chunk" and max(self.size, other.size) % min(self.size, other.size) == 0:
+            return Window("chunk", max(self.size, other.size))
+        if self.kind == other.kind == "sliding":
+            return Window("sliding", max(self.size, other.size))
+        return Window("full")
+
 
 @dataclass(frozen=True)
 class GroupKey:

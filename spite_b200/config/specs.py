@@ -33,9 +33,11 @@ class BlockSpec:
     feed-forward, two mixers."""
     arrangement: str
     parts: dict[str, PartSpec] = field(default_factory=dict)
+    params: dict[str, Any] = field(default_factory=dict)      # constants of the arrangement itself (its constructor's)
 
     def __hash__(self):
-        return hash((self.arrangement, tuple(sorted((k, hash(v)) for k, v in self.parts.items()))))
+        return hash((self.arrangement, tuple(sorted((k, hash(v)) for k, v in self.parts.items())),
+                     repr(sorted(self.params.items()))))
 
     def __getattr__(self, place):
         """`spec.mixer` reads the part at the place `mixer`."""

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int nq = p.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
-    const int heads_total = nq + 2 * nkv;
+    const int heads_total = p.q_only ? nq : nq + 2 * nkv;
     const int head_end = min(heads_total, (int)(blockIdx.y + 1) * heads_per_block);
     const int pos = b.positions[t];
     if (p.gates_out && blockIdx.y == 0)                      // the gate columns behind the heads
@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
             p.gates_out[(size_t)t * nq + h] =
                 1.0f / (1.0f + expf(-to_f32(((const T*)p.qkv)[(size_t)t * p.qkv_stride + (size_t)heads_total * hd + h])));
     int page = -1;
-    if (p.write_cache) {
+    if (p.write_cache && !p.q_only) {
         page = b.block_table[(size_t)b.seg_of_token[t] * b.table_width + pos / c.page_size];
         if (page >= c.n_pages) page = -1;                     // the host never lets this happen
     }
@@ -94,12 +94,14 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
             dst = (T*)c.kv + (is_v ? c.v_offset : 0) +
                   (((size_t)page * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
         }
+        const float* bias = p.bias ? p.bias + (size_t)head * hd : nullptr;
         if (is_v) {
             const T* other = p.v_other ? (const T*)p.v_other + (size_t)t * p.v_other_stride +
                                          (size_t)(head - nq - nkv) * p.v_other_head : nullptr;
             for (int i = lane; 2 * i < hd; i += 32) {
                 float a, bb;
                 load_pair(in + 2 * i, a, bb);
+                if (bias) { a += bias[2 * i]; bb += bias[2 * i + 1]; }
                 if (other) {                                 // blended with the other layer's value of this token
                     if (2 * i < p.v_mix_dim) a = (1.0f - p.v_mix) * a + p.v_mix * to_f32(other[2 * i]);
                     if (2 * i + 1 < p.v_mix_dim) bb = (1.0f - p.v_mix) * bb + p.v_mix * to_f32(other[2 * i + 1]);
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
             if (2 * (lane + 32 * r) < hd) {
                 if (halves) { x0[r] = to_f32(in[e0[r]]); x1[r] = to_f32(in[e1[r]]); }
                 else load_pair(in + e0[r], x0[r], x1[r]);
+                if (bias) { x0[r] += bias[e0[r]]; x1[r] += bias[e1[r]]; }
             }
         }
         if (norm_first) {
@@ -256,7 +259,7 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* given, const St
     if (!c) return SPITE_BAD_ARG;
     QkPrepareParams filled = *given;                          // a caller that leaves the later fields at zero means: rows
     if (filled.qkv_stride == 0)                               // without anything behind the heads, a pure rotation
-        filled.qkv_stride = (long long)(filled.num_heads + 2 * c->num_kv_heads) * c->head_dim;
+        filled.qkv_stride = (long long)(filled.num_heads + (filled.q_only ? 0 : 2 * c->num_kv_heads)) * c->head_dim;
     if (filled.rot_amplitude == 0.f) filled.rot_amplitude = 1.f;
     const QkPrepareParams* p = &filled;
     const int chk = check_common(b, c, p->num_heads);
@@ -264,8 +267,8 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* given, const St
     if (b->n_tokens == 0) return SPITE_OK;
     if (p->pairing != SPITE_PAIR_NEIGHBOURS && p->pairing != SPITE_PAIR_HALVES) return SPITE_BAD_ARG;
     if (p->inv_freq && (p->rotary_dim < 2 || p->rotary_dim % 2 || p->rotary_dim > c->head_dim)) return SPITE_BAD_ARG;
-    if (p->pairing == SPITE_PAIR_HALVES && p->inv_freq && p->rotary_dim % 4) return SPITE_UNSUPPORTED;  // pairs beyond the rotating part start at an even pair index
-    const int heads = p->num_heads + 2 * c->num_kv_heads;
+    const int heads = p->num_heads + (p->q_only ? 0 : 2 * c->num_kv_heads);
+    if (p->q_only && (p->v_other || p->gates_out)) return SPITE_BAD_ARG;
     if (p->qkv_stride < (long long)heads * c->head_dim || (p->qkv_stride & 1)) return SPITE_BAD_ARG;
     if (p->gates_out && p->qkv_stride < (long long)heads * c->head_dim + p->num_heads) return SPITE_BAD_ARG;
     if (p->v_other && (p->v_mix_dim < 0 || p->v_mix_dim > c->head_dim || p->v_other_head < p->v_mix_dim)) return SPITE_BAD_ARG;

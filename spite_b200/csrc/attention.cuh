@@ -57,6 +57,10 @@ struct QkPrepareParams {
     float v_mix;
     // gates_out[t * nq + h] = sigmoid(qkv[t * qkv_stride + (nq + 2 nkv) * head_dim + h]) (null: no gate columns)
     float* gates_out;
+    // bias[column] (float32, the columns of a token's row of qkv up to the last head's) is added to the projection's
+    // output before anything else happens to it (null: none)
+    const float* bias;
+    int q_only;                 // the rows of qkv hold the q heads alone: this layer reads keys and values that another layer cached
 };
 
 struct AttentionParams {

@@ -336,3 +336,200 @@ SPITE_API int spite_rms_norm(int out_dtype, const float* x, const float* gain, c
         SPITE_LAUNCH(rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, gain, rows, (__nv_bfloat16*)y, d, eps);
     return spite_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// A sublayer whose output is normed before it joins the residual stream:
+//     h[m, :] += mult * y[m, :] * rsqrt(mean(y[m]^2) + eps) * gain
+// and, if `next_out` is given, the norm that the next sublayer reads, of the row just made:
+//     next_out[m, :] = h[m, :] * rsqrt(mean(h[m]^2) + eps) * next_gain
+// One block per row; the row (y, then h) stays in registers between the sums and the scalings, VPT groups of four
+// elements a thread.  All sums float32.
+template <typename T, int VPT>
+__global__ void rms_norm_residual_vec_kernel(const float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ h,
+                                             const float* __restrict__ next_gain, T* __restrict__ next_out, int d, float eps,
+                                             float mult) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const size_t m = blockIdx.x;
+    const float4* in = (const float4*)(y + m * d);
+    float4* hr = (float4*)(h + m * d);
+    const int d4 = d >> 2;
+    float4 v[VPT], r[VPT];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = c < d4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        r[k] = c < d4 ? hr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) s += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    s = block_sum(s, scratch);
+    const float scale = 1.0f / sqrtf(s / (float)d + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < d4) {
+            const float4 g = ((const float4*)gain)[c];
+            r[k].x += mult * (v[k].x * scale * g.x); r[k].y += mult * (v[k].y * scale * g.y);
+            r[k].z += mult * (v[k].z * scale * g.z); r[k].w += mult * (v[k].w * scale * g.w);
+            hr[c] = r[k];
+            s2 += (r[k].x * r[k].x + r[k].y * r[k].y) + (r[k].z * r[k].z + r[k].w * r[k].w);
+        }
+    }
+    if (!next_out) return;
+    s2 = block_sum(s2, scratch);
+    const float scale2 = 1.0f / sqrtf(s2 / (float)d + eps);
+    T* out = next_out + m * d;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < d4) {
+            const float4 g = ((const float4*)next_gain)[c];
+            store4(out + 4 * c, r[k].x * scale2 * g.x, r[k].y * scale2 * g.y, r[k].z * scale2 * g.z, r[k].w * scale2 * g.w);
+        }
+    }
+}
+
+// The same for any width: passes over the rows in global memory.
+template <typename T>
+__global__ void rms_norm_residual_kernel(const float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ h,
+                                         const float* __restrict__ next_gain, T* __restrict__ next_out, int d, float eps,
+                                         float mult) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const size_t m = blockIdx.x;
+    const float* in = y + m * d;
+    float* hr = h + m * d;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = in[c]; s += v * v; }
+    s = block_sum(s, scratch);
+    const float scale = 1.0f / sqrtf(s / (float)d + eps);
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float v = hr[c] + mult * (in[c] * scale * gain[c]);
+        hr[c] = v;                                             // (read again below by the thread that wrote it)
+        s2 += v * v;
+    }
+    if (!next_out) return;
+    s2 = block_sum(s2, scratch);
+    const float scale2 = 1.0f / sqrtf(s2 / (float)d + eps);
+    T* out = next_out + m * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(hr[c] * scale2 * next_gain[c]);
+}
+
+SPITE_API int spite_rms_norm_residual(int out_dtype, const float* y, const float* gain, float* h, const float* next_gain,
+                                      void* next_out, int n_rows, int d, float eps, float mult, void* stream) {
+    if (!y || !gain || !h || n_rows < 0 || d <= 0 || !(eps > 0.f) || !(mult == mult)) return SPITE_BAD_ARG;
+    if ((next_out != nullptr) != (next_gain != nullptr)) return SPITE_BAD_ARG;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (n_rows == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool f32 = out_dtype == SPITE_DT_F32;
+    const bool aligned = d % 4 == 0 &&
+        ((((uintptr_t)y | (uintptr_t)gain | (uintptr_t)h | (uintptr_t)next_gain | (uintptr_t)next_out) & 15) == 0);
+    if (aligned && d <= 256 * 4 * 4) {
+        const int d4 = d / 4;
+        const int threads = d4 <= 128 ? 128 : 256;
+        const int vpt = (d4 + threads - 1) / threads;
+#define SPITE_RMSR(V)                                                                                                      \
+        if (f32) SPITE_LAUNCH((rms_norm_residual_vec_kernel<float, V>), n_rows, threads, 0, st, y, gain, h, next_gain,     \
+                              (float*)next_out, d, eps, mult);                                                             \
+        else SPITE_LAUNCH((rms_norm_residual_vec_kernel<__nv_bfloat16, V>), n_rows, threads, 0, st, y, gain, h, next_gain, \
+                          (__nv_bfloat16*)next_out, d, eps, mult)
+        if (vpt <= 1) { SPITE_RMSR(1); }
+        else if (vpt <= 2) { SPITE_RMSR(2); }
+        else { SPITE_RMSR(4); }
+#undef SPITE_RMSR
+        return spite_launch_status();
+    }
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    if (f32) SPITE_LAUNCH(rms_norm_residual_kernel<float>, n_rows, threads, 0, st, y, gain, h, next_gain, (float*)next_out, d, eps, mult);
+    else SPITE_LAUNCH(rms_norm_residual_kernel<__nv_bfloat16>, n_rows, threads, 0, st, y, gain, h, next_gain,
+                      (__nv_bfloat16*)next_out, d, eps, mult);
+    return spite_launch_status();
+}
+
+// out[m, :] (=|+=) vec: a bias that a product then adds its rows to (float32 [n_rows, d]).
+__global__ void fill_rows_kernel(float* __restrict__ out, const float* __restrict__ vec, long long n, int d, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float b = vec[i % d];
+        out[i] = accumulate ? out[i] + b : b;
+    }
+}
+
+SPITE_API int spite_fill_rows(float* out, const float* vec, int n_rows, int d, int accumulate, void* stream) {
+    if (!out || !vec || n_rows < 0 || d <= 0) return SPITE_BAD_ARG;
+    if (n_rows == 0) return SPITE_OK;
+    const long long n = (long long)n_rows * d;
+    const long long blocks = (n + 255) / 256;
+    SPITE_LAUNCH(fill_rows_kernel, (int)(blocks < 8192 ? blocks : 8192), 256, 0, (cudaStream_t)stream, out, vec, n, d, accumulate);
+    return spite_launch_status();
+}
+
+// What stands between a mixer's heads and its output projection:
+//     out[m, h * size + j] = x[m, h * size + j] * r_mh * gain[h * size + j] * sigmoid(gates[m, h * size + j])
+// r_mh = rsqrt(mean_j(x[m, h, :]^2) + eps) if eps > 0, else 1; gain and gates may be null (a factor of one).
+// `gates` has rows of `gate_stride` elements (the gate columns of a wider product).  One warp per (token, head); the
+// head's elements stay in registers between the sum and the scaling while they are few enough.
+template <typename TX, typename TO>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(const TX* __restrict__ x, const TX* __restrict__ gates,
+                                                             long long gate_stride, const float* __restrict__ gain,
+                                                             TO* __restrict__ out, int n_tokens, int heads, int size, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= (long long)n_tokens * heads) return;
+    const long long m = row / heads;
+    const int h = (int)(row % heads);
+    const size_t base = (size_t)m * heads * size + (size_t)h * size;
+    const TX* in = x + base;
+    float mul = 1.f;
+    if (eps > 0.f) {
+        float s = 0.f;
+        for (int j = lane; j < size; j += 32) { const float v = to_f32(in[j]); s += v * v; }
+        s = warp_sum(s);
+        mul = 1.0f / sqrtf(s / (float)size + eps);
+    }
+    const TX* g = gates ? gates + (size_t)m * gate_stride + (size_t)h * size : nullptr;
+    const float* w = gain ? gain + (size_t)h * size : nullptr;
+    TO* o = out + base;
+    for (int j = lane; j < size; j += 32) {
+        float v = to_f32(in[j]) * mul;
+        if (w) v *= w[j];
+        if (g) v *= 1.0f / (1.0f + expf(-to_f32(g[j])));
+        o[j] = from_f32<TO>(v);
+    }
+}
+
+// x_dtype: type of x and gates; out_dtype: type of out (x may be the float32 result of a recurrence while out feeds a
+// bfloat16 product); out may be x.
+SPITE_API int spite_head_norm_gate(int x_dtype, int out_dtype, const void* x, const void* gates, long long gate_stride,
+                                   const float* gain, void* out, int n_tokens, int heads, int size, float eps, void* stream) {
+    if (!x || !out || n_tokens < 0 || heads < 1 || size < 1 || !(eps == eps) || eps < 0.f) return SPITE_BAD_ARG;
+    if (gates && gate_stride < (long long)heads * size) return SPITE_BAD_ARG;
+    if (x_dtype != SPITE_DT_F32 && x_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (x_dtype == SPITE_DT_BF16 && out_dtype == SPITE_DT_F32) return SPITE_UNSUPPORTED;
+    if (n_tokens == 0) return SPITE_OK;
+    const long long rows = (long long)n_tokens * heads;
+    const long long blocks = (rows + 3) / 4;
+    if (blocks > 0x7fffffffLL) return SPITE_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == SPITE_DT_F32 && out_dtype == SPITE_DT_F32)
+        SPITE_LAUNCH((head_norm_gate_kernel<float, float>), (int)blocks, 128, 0, st, (const float*)x, (const float*)gates,
+                     gate_stride, gain, (float*)out, n_tokens, heads, size, eps);
+    else if (x_dtype == SPITE_DT_F32)
+        SPITE_LAUNCH((head_norm_gate_kernel<float, __nv_bfloat16>), (int)blocks, 128, 0, st, (const float*)x, (const float*)gates,
+                     gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps);
+    else
+        SPITE_LAUNCH((head_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16>), (int)blocks, 128, 0, st, (const __nv_bfloat16*)x,
+                     (const __nv_bfloat16*)gates, gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps);
+    return spite_launch_status();
+}

@@ -35,15 +35,18 @@ struct GemmParams {
 
 #define SPITE_ACT_NONE 0
 #define SPITE_ACT_RELU2 1        // relu(y)^2
+#define SPITE_ACT_GELU_TANH 2    // 0.5 y (1 + tanh(sqrt(2/pi) (y + 0.044715 y^3)))
 
 __device__ __forceinline__ float apply_activation(int act, float y) {
     if (act == SPITE_ACT_RELU2) { y = fmaxf(y, 0.f); y *= y; }
+    else if (act == SPITE_ACT_GELU_TANH) y = 0.5f * y * (1.0f + tanhf(0.7978845608028654f * (y + 0.044715f * y * y * y)));
     return y;
 }
 
 // An activation goes with the plain store only.
 static inline bool activation_ok(const GemmParams* p) {
-    return p->activation == SPITE_ACT_NONE || (p->activation == SPITE_ACT_RELU2 && p->epilogue == EPI_STORE);
+    return p->activation == SPITE_ACT_NONE ||
+           ((p->activation == SPITE_ACT_RELU2 || p->activation == SPITE_ACT_GELU_TANH) && p->epilogue == EPI_STORE);
 }
 
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }

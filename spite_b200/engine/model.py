@@ -45,7 +45,7 @@ class Model:
         for spec in plan.blocks:
             if spec.arrangement not in blocks:
                 raise ConfigError(f"no block arrangement {spec.arrangement!r}; known: {', '.join(sorted(blocks))}")
-            self.blocks.append(blocks[spec.arrangement](self.ctx, spec))
+            self.blocks.append(blocks[spec.arrangement](self.ctx, spec, **spec.params))
         self.junctions = [build_part("junction", spec, self.ctx) for spec in plan.junctions]
         self.final_norm = build_part("norm", plan.final_norm, self.ctx)
         self.embed_table = None
@@ -101,6 +101,13 @@ class Model:
             have = self._cache_specs.get(call.cache)
             if have is None:
                 self._cache_specs[call.cache] = req
+                continue
+            a, b = have[0], req[0]
+            if a is not None and b is not None and a.window != b.window and have[1] == req[1] \
+                    and (a.num_kv_heads, a.head_dim, a.planes) == (b.num_kv_heads, b.head_dim, b.planes):
+                # layers that read one cache through different windows: every layer masks by its own, and the pages go
+                # back by the rule that keeps what either still reads
+                self._cache_specs[call.cache] = (PagedKV(a.window.union(b.window), a.num_kv_heads, a.head_dim, a.planes), have[1])
             elif have != req:
                 raise ConfigError(
                     f"cache {call.cache} is shared by layers whose mixers need different caches: {have} vs {req}")

@@ -69,12 +69,30 @@ class KernelSet:
         h float32 [*, d], gain float32 [d]."""
         raise NotImplementedError
 
+    def rms_norm_residual(self, y, gain, eps, mult, h, *, next_gain=None, next_out=None):
+        """A sublayer's output is normed before it joins the residual stream:
+        h[m, :] += mult * y[m, :] * rsqrt(mean(y[m]^2) + eps) * gain (y, h float32 [M, d]); with `next_out` [M, d]
+        (T) also the norm the next sublayer reads, of the row just made: next_out = h * rsqrt(mean(h^2) + eps) * next_gain."""
+        raise NotImplementedError
+
+    def fill_rows(self, out, vec, *, accumulate=False):
+        """out[m, :] (float32 [M, d]) = vec (float32 [d]), or += vec: a bias laid down for a product that adds to it."""
+        raise NotImplementedError
+
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+        """What stands between a mixer's heads and its output projection.  x [M, heads * size] (T, or float32: the
+        result of a recurrence), out [M, heads * size] (T; may be x):
+        out[m, h, j] = x[m, h, j] * r * gain[h * size + j] * sigmoid(gates[m, gate_column + h * size + j]) with
+        r = rsqrt(mean_j x[m, h, :]^2 + eps) if `eps` is given (a norm of every head without a gain of its own), else 1;
+        `gates` (a 2-D tensor of x's type, the gate columns of a wider product) and `gain` (float32) may be left out."""
+        raise NotImplementedError
+
     # ---- matrix products: y = x W^T with W [out, in]
     def linear(self, x, w, out, *, accumulate=False, row_scale=None, activation=None):
         """out[M, N] = x[M, K] @ w[N, K]^T.  `out` is T, or float32 (logits); with
         `accumulate` it is float32 and the product is added to it (residual stream).
-        `row_scale` [M] float32 multiplies the product's rows.  `activation` "relu2" (with an
-        output of type T): out = relu(s y)^2."""
+        `row_scale` [M] float32 multiplies the product's rows.  `activation` (with an output of type T):
+        "relu2": out = relu(s y)^2; "gelu_tanh": out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), z = s y."""
         raise NotImplementedError
 
     def linear_swiglu(self, x, w_gate_up, out, *, row_scale=None):
@@ -112,8 +130,10 @@ class KernelSet:
 
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None):
+                   value_mix=None, gates_out=None, bias=None, q_only=False):
         """Encode positions of q and k, normalise, scale q, append k and v to the cache.
+        `bias` float32 [(nq + 2 nkv) hd]: added to the projection's columns before anything else.  `q_only`: a row of
+        qkv holds the q heads alone (and `bias` theirs): the layer reads keys and values that another layer cached.
         qkv [M, >= (nq + 2 nkv) hd] T -> q_out [M, nq hd] T; `cache` is a `LayerCache`.
         `rotation`: a `parts.Rotation` or None; `qk_norm`: a `parts.QkNorm` or None (RMS norm of
         every q and k head, after the rotation unless it says before); `temperature`:
@@ -156,6 +176,24 @@ class KernelSet:
         head: rows_out[h M + m] = m nq + h, offsets_out[h] = h M (int32 [nq M] and [nq + 1]); `sorted_out` [nq M, head_dim]
         (T), if given, receives the heads' unrotated parts in that order: sorted_out[h M + m] = q[m, h, :head_dim]."""
         raise NotImplementedError
+
+    # ---- recurrent mixers
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+        """Matrix memory with exponential gates, token by token, for every segment of the step from the state its
+        request's slot holds (all zeros: the start of a sequence); the slot receives the state after the segment's
+        last token.  proj float32 [M, *] holds, from the columns `columns` = (q, k, v, i, f) on, q and k
+        [heads * dim], v [heads * vdim] and the gates' pre-activations [heads]; out float32 [M, heads * vdim];
+        state float32 [slots, heads, `mlstm_state_size(dim, vdim)`].
+        i = cap tanh((a + i_bias) / cap), f = logsigmoid(cap tanh((c + f_bias) / cap)), m' = max(f + m, i),
+        S' = exp(f + m - m') S + exp(i - m') k v^T, n' alike with k, out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6),
+        q times `q_scale`.  All float32."""
+        raise NotImplementedError
+
+    @staticmethod
+    def mlstm_state_size(dim: int, vdim: int) -> int:
+        """Floats of one head's state: S [dim, vdim], then one copy of (n [dim], m) for every 32 value columns, each
+        rounded up to a multiple of four floats."""
+        return dim * vdim + -(-vdim // 32) * (-(-(dim + 1) // 4) * 4)
 
     # ---- mixture of experts
     def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:

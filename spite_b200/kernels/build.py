@@ -40,6 +40,7 @@ LIBRARIES = {
     "attention_tc": (["attention_tc.cu"], []),
     "moe": (["moe.cu"], []),
     "latent": (["latent.cu"], []),
+    "recurrent": (["recurrent.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

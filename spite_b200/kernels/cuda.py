@@ -20,7 +20,7 @@ _STATUS = {-1: "malformed argument", -2: "size not supported by this kernel", -3
 
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
 _WINDOW = {"full": 0, "chunk": 1, "sliding": 2}
-_ACTIVATION = {None: 0, "relu2": 1}
+_ACTIVATION = {None: 0, "relu2": 1, "gelu_tanh": 2}
 
 
 class GemmParams(C.Structure):
@@ -50,7 +50,8 @@ class QkPrepareParams(C.Structure):
                 ("temperature_scale", C.c_float), ("num_heads", C.c_int), ("write_cache", C.c_int),
                 ("qkv_stride", C.c_longlong), ("rot_amplitude", C.c_float),
                 ("v_other", C.c_void_p), ("v_other_stride", C.c_longlong), ("v_other_head", C.c_int),
-                ("v_mix_dim", C.c_int), ("v_mix", C.c_float), ("gates_out", C.c_void_p)]
+                ("v_mix_dim", C.c_int), ("v_mix", C.c_float), ("gates_out", C.c_void_p),
+                ("bias", C.c_void_p), ("q_only", C.c_int)]
 
 
 class AttentionParams(C.Structure):
@@ -74,6 +75,15 @@ class LatentQueryParams(C.Structure):
                 ("num_heads", C.c_int), ("head_dim", C.c_int), ("rot_dim", C.c_int), ("kv_rank", C.c_int),
                 ("row", C.c_int), ("positions", C.c_void_p), ("n_tokens", C.c_int),
                 ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p), ("q_sorted_out", C.c_void_p)]
+
+
+class MlstmParams(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("stride", C.c_longlong),
+                ("q_col", C.c_int), ("k_col", C.c_int), ("v_col", C.c_int), ("i_col", C.c_int), ("f_col", C.c_int),
+                ("i_bias", C.c_void_p), ("f_bias", C.c_void_p), ("out", C.c_void_p), ("state", C.c_void_p),
+                ("head_stride", C.c_longlong), ("cu_seqlens", C.c_void_p), ("slots", C.c_void_p),
+                ("n_segments", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
+                ("gate_cap", C.c_float), ("q_scale", C.c_float)]
 
 
 class AttnMmaExtra(C.Structure):
@@ -350,6 +360,56 @@ class CudaKernels(KernelSet):
         self._count("elementwise", 1)
         _check(st, "rms_norm")
 
+    def rms_norm_residual(self, y, gain, eps, mult, h, *, next_gain=None, next_out=None):
+        self._t(y, torch.float32, "y"); self._t(h, torch.float32, "h"); self._t(gain, torch.float32, "gain")
+        M, d = h.shape
+        if tuple(y.shape) != (M, d) or gain.numel() != d:
+            raise KernelError("rms_norm_residual: shapes do not fit")
+        if (next_out is None) != (next_gain is None):
+            raise KernelError("rms_norm_residual: the next norm needs its gain and its output")
+        if next_out is not None:
+            self._t(next_out, None, "next_out"); self._t(next_gain, torch.float32, "next_gain")
+            if tuple(next_out.shape) != (M, d) or next_gain.numel() != d or next_out.dtype not in _DT:
+                raise KernelError("rms_norm_residual: the next norm's output or gain does not fit")
+        st = self._lib("elementwise").spite_rms_norm_residual(
+            _DT[next_out.dtype] if next_out is not None else self._dt, C.c_void_p(y.data_ptr()), C.c_void_p(gain.data_ptr()),
+            C.c_void_p(h.data_ptr()), C.c_void_p(_ptr(next_gain)), C.c_void_p(_ptr(next_out)), M, d, C.c_float(eps),
+            C.c_float(mult), self._stream())
+        self._count("elementwise", 1)
+        _check(st, "rms_norm_residual")
+
+    def fill_rows(self, out, vec, *, accumulate=False):
+        self._t(out, torch.float32, "out"); self._t(vec, torch.float32, "vec")
+        M, d = out.shape
+        if vec.numel() != d:
+            raise KernelError("fill_rows: the vector must have the rows' width")
+        st = self._lib("elementwise").spite_fill_rows(C.c_void_p(out.data_ptr()), C.c_void_p(vec.data_ptr()), M, d,
+                                                      int(bool(accumulate)), self._stream())
+        self._count("elementwise", 1)
+        _check(st, "fill_rows")
+
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+        self._t(x, None, "x"); self._t(out, self.dtype, "out")
+        if x.dtype not in (self.dtype, torch.float32):
+            raise KernelError(f"head_norm_gate: x must be {self.dtype} or float32")
+        M = x.shape[0]
+        if tuple(x.shape) != (M, heads * size) or tuple(out.shape) != (M, heads * size):
+            raise KernelError("head_norm_gate: x and out must be [tokens, heads * size]")
+        g_ptr, g_stride = None, 0
+        if gates is not None:
+            self._t(gates, x.dtype, "gates")
+            if gates.dim() != 2 or gates.shape[0] != M or gate_column < 0 or gate_column + heads * size > gates.shape[1]:
+                raise KernelError("head_norm_gate: the gate columns do not fit")
+            g_ptr, g_stride = gates.data_ptr() + int(gate_column) * gates.element_size(), gates.shape[1]
+        if gain is not None and self._t(gain, torch.float32, "gain").numel() != heads * size:
+            raise KernelError("head_norm_gate: the gain must have heads * size elements")
+        st = self._lib("elementwise").spite_head_norm_gate(
+            _DT[x.dtype], self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(g_ptr), C.c_longlong(g_stride),
+            C.c_void_p(_ptr(gain)), C.c_void_p(out.data_ptr()), M, int(heads), int(size), C.c_float(eps or 0.0),
+            self._stream())
+        self._count("elementwise", 1)
+        _check(st, "head_norm_gate")
+
     def clear_pages(self, kv, page_ids):
         self._t(kv, None, "cache")
         if not page_ids:
@@ -619,9 +679,16 @@ class CudaKernels(KernelSet):
                           page_size=kv.shape[3], num_kv_heads=kv.shape[2], head_dim=kv.shape[4])
 
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None):
+                   value_mix=None, gates_out=None, bias=None, q_only=False):
         self._t(qkv, self.dtype, "qkv"); self._t(q_out, self.dtype, "q_out")
         head_dim = cache.kv.shape[4]
+        n_cols = (num_heads + (0 if q_only else 2 * cache.kv.shape[2])) * head_dim
+        if qkv.shape[1] < n_cols:
+            raise KernelError(f"qk_prepare: rows of {qkv.shape[1]} elements cannot hold the heads' {n_cols}")
+        if bias is not None and self._t(bias, torch.float32, "bias").numel() != n_cols:
+            raise KernelError(f"qk_prepare: the bias has {bias.numel()} elements, the heads have {n_cols}")
+        if q_only and cache.write:
+            raise KernelError("qk_prepare: a layer without keys and values of its own cannot append to the cache")
         if cache.kv.shape[0] != 2:
             raise KernelError("qk_prepare appends keys and values: the cache needs both planes")
         inv_freq, pairing, rotary_dim, amplitude = None, 0, head_dim, 1.0
@@ -657,7 +724,7 @@ class CudaKernels(KernelSet):
                             temperature_floor=floor, temperature_scale=scale, num_heads=num_heads,
                             write_cache=int(cache.write), qkv_stride=qkv.shape[1], rot_amplitude=amplitude,
                             v_other=v_other, v_other_stride=v_stride, v_other_head=int(v_head), v_mix_dim=int(v_dim),
-                            v_mix=float(v_lam), gates_out=_ptr(gates_out))
+                            v_mix=float(v_lam), gates_out=_ptr(gates_out), bias=_ptr(bias), q_only=int(bool(q_only)))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
         self._count("attention", 1)
@@ -840,6 +907,27 @@ class CudaKernels(KernelSet):
         st = self._lib("latent").spite_latent_queries(self._dt, C.byref(p), self._stream())
         self._count("latent", 1)
         _check(st, "latent_queries")
+
+    # ------------------------------------------------------------------ recurrent mixers
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+        self._t(proj, torch.float32, "proj"); self._t(out, torch.float32, "out"); self._t(state, torch.float32, "state")
+        self._t(i_bias, torch.float32, "i_bias"); self._t(f_bias, torch.float32, "f_bias")
+        M = proj.shape[0]
+        q_col, k_col, v_col, i_col, f_col = (int(c) for c in columns)
+        if tuple(out.shape) != (M, heads * vdim) or state.dim() != 3 or state.shape[1] != heads \
+                or state.shape[2] < self.mlstm_state_size(dim, vdim) or i_bias.numel() != heads or f_bias.numel() != heads:
+            raise KernelError("mlstm_scan: shapes do not fit")
+        if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim, i_col + heads, f_col + heads) > proj.shape[1]:
+            raise KernelError("mlstm_scan: the columns lie outside the projection's rows")
+        n_seg = batch.cu_seqlens.numel() - 1
+        p = MlstmParams(proj=proj.data_ptr(), stride=proj.shape[1], q_col=q_col, k_col=k_col, v_col=v_col, i_col=i_col,
+                        f_col=f_col, i_bias=i_bias.data_ptr(), f_bias=f_bias.data_ptr(), out=out.data_ptr(),
+                        state=state.data_ptr(), head_stride=state.shape[2], cu_seqlens=batch.cu_seqlens.data_ptr(),
+                        slots=batch.slots.data_ptr(), n_segments=n_seg, heads=int(heads), dim=int(dim), vdim=int(vdim),
+                        gate_cap=float(gate_cap), q_scale=float(q_scale))
+        st = self._lib("recurrent").spite_mlstm_scan(C.byref(p), self._stream())
+        self._count("recurrent", 1)
+        _check(st, "mlstm_scan")
 
     # ------------------------------------------------------------------ mixture of experts
     def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:

@@ -5,8 +5,10 @@ the query's chunk, the last W keys), the position encoding, the per-head norm of
 q and k (after or before the rotation, with gains or without), the
 temperature factor, a value size that differs from the key size, a sink in
 the softmax (an extra term exp(sink) in the sum, with nothing behind it; one score for all heads or a learned
-one per head), a bias that grows with the distance between query and key, a gate on every head's output and the
-blending of the values with those of another layer are constructor parameters.
+one per head), a bias that grows with the distance between query and key, a gate on every head's output (one
+number a head, or one for every element of the concatenated heads), biases on the four projections, the
+blending of the values with those of another layer, and keys and values that are not the layer's own but those
+another layer cached are constructor parameters.
 
 Formulas: crates/spite-models/src/llama/llama4.rs:126-207 (projections, rotation
 then norm, temperature factor on layers without rotation, append to the cache,
@@ -27,13 +29,14 @@ from .base import Mixer, ParamSpec, QkNorm, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
+    can_store = True
     kernel_libraries = ("gemm_simt", "attention", "attention_mma", "attention_rows", "attention_tc", "attention_decode")
 
     def __init__(self, ctx, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window=("full", 0), qk_norm_eps=None, qk_norm_gain=False,
                  qk_norm_before_rotation=False, temperature_tuning=None, softmax_scale=None,
                  value_dim=None, sink_logit=None, head_sinks=False, distance_slopes=None, head_gate=False,
-                 value_mix=None):
+                 value_mix=None, bias=False, output_gate=False, kv_shared=False):
         """`head_dim` is the size of a query and a key head, `value_dim` that of a value head (default: the
         same).  `sink_logit`, if given, is the score of a sink: a term exp(sink) in every softmax's sum that adds
         nothing to the output, p_j = exp(s_j) / (exp(sink) + sum exp(s_j')); with `head_sinks` the score is a
@@ -41,8 +44,18 @@ class PagedAttention(Mixer):
         is taken off the score of query position i and key position j.  `head_gate`: head h's output is multiplied by
         sigmoid(w_h . x), w the rows of `gate_proj` [heads, hidden], x the mixer's input.  `value_mix`: "source"
         marks the layer whose values of the step's tokens later layers blend in; "blend" makes this layer's
-        values (1 - lam) v + lam v_source before they are cached, lam the scalar parameter `value_mix`."""
+        values (1 - lam) v + lam v_source before they are cached, lam the scalar parameter `value_mix`.
+        `bias`: the projections of q, k, v and the output projection add a bias each (`q_bias`, `k_bias`, `v_bias`,
+        `o_bias`).  `output_gate`: the concatenated heads are multiplied element by element by sigmoid(W x), W the
+        parameter `out_gate_proj` [heads * value size, hidden], x the mixer's input, before the output projection.
+        `kv_shared`: the layer has no key and value projections; it reads the cache another layer of the run order
+        writes (keys after that layer's rotation) with its own queries, window and everything else."""
         super().__init__(ctx)
+        self.has_bias, self.output_gate, self.kv_shared = bool(bias), bool(output_gate), bool(kv_shared)
+        if self.kv_shared and value_mix:
+            raise ConfigError("a layer that reads another layer's keys and values has no values to blend")
+        if self.output_gate and head_gate:
+            raise ConfigError("a gate per head and a gate per element exclude each other")
         if num_heads % num_kv_heads:
             raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads evenly")
         if head_dim < 1 or head_dim > 256:
@@ -73,7 +86,11 @@ class PagedAttention(Mixer):
         # elements are exact zeros: they add nothing to a score and come out of the attention as zeros.
         # A rotation or a per-head norm would have to know which elements of a row are padding: a layer
         # with either keeps its rows as they are.
-        may_pad = qk_norm_eps is None and self.position.rotation() is None
+        # (A rotation of the leading elements alone leaves the padding, which follows the key's last element, alone too.)
+        rot = self.position.rotation()
+        if rot is not None and (rot.rotary_dim or self.kd) > self.kd:
+            raise ConfigError(f"{rot.rotary_dim} rotating elements in a head of {self.kd}")
+        may_pad = qk_norm_eps is None and (rot is None or rot.rotary_dim is not None)
         if self.kd % 2 and not may_pad:
             raise ConfigError(f"head_dim {head_dim} must be even where heads rotate or are normed")
         hd = max(self.kd, self.vd)
@@ -104,8 +121,15 @@ class PagedAttention(Mixer):
 
     def param_specs(self):
         d, nq, nkv, kd, vd = self.d, self.nq, self.nkv, self.kd, self.vd
-        specs = {"q_proj": ParamSpec((nq * kd, d)), "k_proj": ParamSpec((nkv * kd, d)),
-                 "v_proj": ParamSpec((nkv * vd, d)), "o_proj": ParamSpec((d, nq * vd))}
+        specs = {"q_proj": ParamSpec((nq * kd, d)), "o_proj": ParamSpec((d, nq * vd))}
+        if not self.kv_shared:
+            specs.update({"k_proj": ParamSpec((nkv * kd, d)), "v_proj": ParamSpec((nkv * vd, d))})
+        if self.has_bias:
+            specs.update({"q_bias": ParamSpec((nq * kd,)), "o_bias": ParamSpec((d,))})
+            if not self.kv_shared:
+                specs.update({"k_bias": ParamSpec((nkv * kd,)), "v_bias": ParamSpec((nkv * vd,))})
+        if self.output_gate:
+            specs["out_gate_proj"] = ParamSpec((nq * vd, d))
         if self.qk_norm_gain:
             specs.update({"q_norm": ParamSpec((kd,), "ones"), "k_norm": ParamSpec((kd,), "ones")})
         if self.has_head_sinks:
@@ -127,9 +151,26 @@ class PagedAttention(Mixer):
     def bind(self, params):
         dt = self.ctx.dtype
         # q, k and v rows in one matrix: one product per layer instead of three
-        rows = [self._pad_heads(params["q_proj"].to(dt), self.nq, self.kd),
-                self._pad_heads(params["k_proj"].to(dt), self.nkv, self.kd),
-                self._pad_heads(params["v_proj"].to(dt), self.nkv, self.vd)]
+        rows = [self._pad_heads(params["q_proj"].to(dt), self.nq, self.kd)]
+        if not self.kv_shared:
+            rows += [self._pad_heads(params["k_proj"].to(dt), self.nkv, self.kd),
+                     self._pad_heads(params["v_proj"].to(dt), self.nkv, self.vd)]
+        self.head_columns = sum(r.shape[0] for r in rows)       # the gates' columns of the product follow the heads'
+        self.qkv_bias = self.o_bias = None
+        if self.has_bias:
+            # added in float32 to the product's columns by the prepare kernel (zeros for the padding), and laid down
+            # in the output buffer before the output projection adds to it
+            def column(name, heads, size):
+                return self._pad_heads(params[name].to(torch.float32).reshape(-1, 1), heads, size).reshape(-1)
+            cols = [column("q_bias", self.nq, self.kd)]
+            if not self.kv_shared:
+                cols += [column("k_bias", self.nkv, self.kd), column("v_bias", self.nkv, self.vd)]
+            self.qkv_bias = torch.cat(cols).contiguous()
+            self.o_bias = params["o_bias"].to(torch.float32).contiguous()
+        if self.output_gate:
+            # a gate per element of the concatenated heads: its rows ride in the same product, laid out like the
+            # attention's result (zero rows for the padding: they meet zeros there)
+            rows.append(self._pad_heads(params["out_gate_proj"].to(dt), self.nq, self.vd))
         if self.head_gate:
             # the gates' rows ride in the same product: one more column per head, then zero rows up to a multiple of 8
             g = params["gate_proj"].to(dt)
@@ -152,7 +193,7 @@ class PagedAttention(Mixer):
     def cache_request(self):
         return PagedKV(self.window, self.nkv, self.hd), None
 
-    def forward(self, x, h, batch, cache):
+    def forward(self, x, h, batch, cache, accumulate=True):
         M = x.shape[0]
         k = self.k
         qkv = torch.empty((M, self.wqkv.shape[0]), dtype=x.dtype, device=x.device)
@@ -172,6 +213,12 @@ class PagedAttention(Mixer):
             if src is None or src[3] != self.nkv:
                 raise ConfigError("a layer blends values in, but no layer before it in the run order is their source")
             extra["value_mix"] = (src[0], src[1], src[2], self.vd, self.value_lambda)
+        if self.qkv_bias is not None:
+            extra["bias"] = self.qkv_bias
+        if self.kv_shared:
+            if cache.write:
+                raise ConfigError("a layer without keys and values of its own was given a cache to write")
+            extra["q_only"] = True
         k.qk_prepare(qkv, q, batch, cache, num_heads=self.nq, rotation=self.position.rotation(),
                      qk_norm=self.qk_norm, temperature=self.temperature, **extra)
         o = torch.empty_like(q)
@@ -186,4 +233,9 @@ class PagedAttention(Mixer):
             more["head_gates"] = gates
         k.paged_attention(q, o, batch, cache, num_heads=self.nq, window=self.window,
                           softmax_scale=self.softmax_scale, cache_settled=True, sink_logit=self.sink_logit, **more)
-        k.linear(o, self.wo, h, accumulate=True)
+        if self.output_gate:
+            k.head_norm_gate(o, o, heads=self.nq, size=self.hd, gates=qkv, gate_column=self.head_columns)
+        if self.o_bias is not None:
+            k.fill_rows(h, self.o_bias, accumulate=accumulate)
+            accumulate = True
+        k.linear(o, self.wo, h, accumulate=accumulate)

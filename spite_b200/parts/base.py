@@ -157,6 +157,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: `forward(..., accumulate=False)` is understood: the part then overwrites `h` (a float32 buffer of the residual
+    #: stream's shape that holds nothing yet) with its output instead of adding to it.  An arrangement that norms a
+    #: sublayer's output before it joins the stream asks for this; for parts without it the arrangement zeroes the buffer.
+    can_store = False
+
     def cache_request(self):
         """(PagedKV | None, FixedState | None): what one cache of this mixer holds."""
         return None, None
@@ -166,6 +171,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    can_store = False            # as for mixers
+
     def forward(self, x, h, batch):
         raise NotImplementedError
 

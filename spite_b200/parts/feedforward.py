@@ -173,12 +173,14 @@ class MoESigmoidPrescaled(FeedForward):
 
 @register_feed_forward("dense_activation")
 class DenseActivation(FeedForward):
-    """h += down( act(up x) ) without a gate; `activation` "relu2": act(z) = relu(z)^2, applied to the float32
-    sums of the first product before they are rounded."""
+    """h += down( act(up x) ) without a gate; `activation` "relu2": act(z) = relu(z)^2; "gelu_tanh":
+    act(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); applied to the float32 sums of the first product
+    before they are rounded."""
     graph_safe = True
+    can_store = True
     kernel_libraries = ("gemm_simt",)
 
-    ACTIVATIONS = ("relu2",)
+    ACTIVATIONS = ("relu2", "gelu_tanh")
 
     def __init__(self, ctx, hidden_size: int, intermediate_size: int, activation: str = "relu2"):
         super().__init__(ctx)
@@ -198,10 +200,10 @@ class DenseActivation(FeedForward):
     def weight_bytes(self):
         return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    def forward(self, x, h, batch):
+    def forward(self, x, h, batch, accumulate=True):
         a = torch.empty((x.shape[0], self.f), dtype=x.dtype, device=x.device)
         self.k.linear(x, self.w_up, a, activation=self.activation)
-        self.k.linear(a, self.w_down, h, accumulate=True)
+        self.k.linear(a, self.w_down, h, accumulate=accumulate)
 
 
 @register_feed_forward("moe_softmax_topk")

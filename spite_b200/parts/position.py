@@ -107,3 +107,28 @@ class RotaryYarn(PositionEncoding):
 
     def rotation(self):
         return self._rotation
+
+
+@register_position("rotary_halves")
+class RotaryHalves(PositionEncoding):
+    """Rotation of the first `rotary_dim` elements of every head of q and k, element i paired with element
+    i + rotary_dim / 2; the other elements pass unchanged.  f_i = theta^(-2i / rotary_dim), optionally rescaled by
+    wavelength as `rotary_frequencies` describes, with `scaling` = {factor, low, high, original}."""
+    graph_safe = True
+
+    def __init__(self, ctx, rotary_dim: int, theta: float, scaling: dict | None = None):
+        super().__init__(ctx)
+        if rotary_dim % 2 or rotary_dim < 2:
+            raise ConfigError("a rotation needs an even number of elements")
+        if scaling:
+            missing = [k for k in ("factor", "low", "high", "original") if k not in scaling]
+            if missing:
+                raise ConfigError(f"rotation scaling lacks {missing}")
+            scaling = {"factor": scaling["factor"], "low_freq_factor": scaling["low"], "high_freq_factor": scaling["high"],
+                       "original_max_position_embeddings": scaling["original"]}
+        f = rotary_frequencies(int(rotary_dim), float(theta), scaling)
+        self._rotation = Rotation(torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device), "halves",
+                                  int(rotary_dim))
+
+    def rotation(self):
+        return self._rotation

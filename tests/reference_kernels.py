@@ -50,6 +50,66 @@ class TorchReferenceKernels(KernelSet):
         y = x * (1.0 / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)) * gain.to(self.acc)
         out.copy_(y.to(out.dtype))
 
+    def rms_norm_residual(self, y, gain, eps, mult, h, *, next_gain=None, next_out=None):
+        v = y.to(self.acc)
+        v = v * (1.0 / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)) * gain.to(self.acc)
+        h.add_((mult * v).to(h.dtype))
+        if next_out is not None:
+            self.rms_norm(h, next_gain, eps, next_out)
+
+    def fill_rows(self, out, vec, *, accumulate=False):
+        if accumulate:
+            out.add_(vec[None, :].to(out.dtype))
+        else:
+            out.copy_(vec[None, :].to(out.dtype).expand_as(out))
+
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+        M = x.shape[0]
+        v = x.to(self.acc).reshape(M, heads, size)
+        if eps is not None:
+            v = v * (1.0 / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps))
+        v = v.reshape(M, heads * size)
+        if gain is not None:
+            v = v * gain.to(self.acc)
+        if gates is not None:
+            v = v * torch.sigmoid(gates[:, gate_column:gate_column + heads * size].to(self.acc))
+        out.copy_(v.to(out.dtype))
+
+    # ---- recurrent mixers
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+        qc, kc, vc, ic, fc = columns
+        x = proj.to(self.acc)
+        cu = batch.cu_seqlens.tolist()
+        slots = batch.slots.tolist()
+        nm = -(-(dim + 1) // 4) * 4
+        for s in range(len(cu) - 1):
+            if s > 0 and slots[s] == slots[0]:                  # a padding copy of the first row
+                out[cu[s]:cu[s + 1]] = 0
+                continue
+            for a in range(heads):
+                st = state[slots[s], a]
+                S = st[:dim * vdim].to(self.acc).reshape(dim, vdim).clone()
+                n = st[dim * vdim:dim * vdim + dim].to(self.acc).clone()
+                m = st[dim * vdim + dim].to(self.acc).clone()
+                for t in range(cu[s], cu[s + 1]):
+                    q = x[t, qc + a * dim:qc + (a + 1) * dim] * q_scale
+                    k = x[t, kc + a * dim:kc + (a + 1) * dim]
+                    v = x[t, vc + a * vdim:vc + (a + 1) * vdim]
+                    ig = gate_cap * torch.tanh((x[t, ic + a] + i_bias[a].to(self.acc)) / gate_cap)
+                    fg = torch.nn.functional.logsigmoid(gate_cap * torch.tanh((x[t, fc + a] + f_bias[a].to(self.acc)) / gate_cap))
+                    m_new = torch.maximum(fg + m, ig)
+                    keep, take = torch.exp(fg + m - m_new), torch.exp(ig - m_new)
+                    S = keep * S + take * torch.outer(k, v)
+                    n = keep * n + take * k
+                    m = m_new
+                    den = torch.maximum((n @ q).abs(), torch.exp(-m)) + 1e-6
+                    out[t, a * vdim:(a + 1) * vdim] = ((S.T @ q) / den).to(out.dtype)
+                st[:dim * vdim] = S.reshape(-1).to(st.dtype)
+                for b in range(-(-vdim // 32)):                  # every block of 32 value columns keeps its own n and m
+                    o = dim * vdim + b * nm
+                    st[o:o + dim] = n.to(st.dtype)
+                    st[o + dim] = m.to(st.dtype)
+
     # ---- matrix products
     def _mm(self, x, w):
         return x.to(self.acc) @ w.to(self.acc).T
@@ -59,8 +119,11 @@ class TorchReferenceKernels(KernelSet):
         if row_scale is not None:
             y = y * row_scale.to(self.acc)[:, None]
         if activation is not None:
-            assert activation == "relu2" and not accumulate
-            y = torch.relu(y) ** 2
+            assert activation in ("relu2", "gelu_tanh") and not accumulate
+            if activation == "relu2":
+                y = torch.relu(y) ** 2
+            else:
+                y = 0.5 * y * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (y + 0.044715 * y ** 3)))
         if accumulate:
             out.add_(y.to(out.dtype))
         else:
@@ -131,14 +194,20 @@ class TorchReferenceKernels(KernelSet):
 
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None):
+                   value_mix=None, gates_out=None, bias=None, q_only=False):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
         M = qkv.shape[0]
-        cols = (nq + 2 * nkv) * hd
-        x = qkv[:, :cols].to(self.acc).reshape(M, nq + 2 * nkv, hd)
+        cols = (nq + (0 if q_only else 2 * nkv)) * hd
+        x = qkv[:, :cols].to(self.acc)
+        if bias is not None:
+            x = x + bias.to(self.acc)[None, :]
+        x = x.reshape(M, -1, hd)
         q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
+        if q_only:
+            assert not cache.write
+            k = q[:, :0]
         pos = batch.positions.long()
         if gates_out is not None:
             gates_out.copy_(torch.sigmoid(qkv[:, cols:cols + nq].to(torch.float32)))
