@@ -53,7 +53,7 @@ class GatedAttention:
     dim: int                       # size of a query and a key head
     vdim: int                      # size of a value head
     scale: float                   # scores are (q . k) * scale
-    chunk: int                     # mask.size
+    chunk: Optional[int]           # mask.size; None: every earlier position is visible
     rot_dims: int
     rot_base: float
     rot_scaling: Optional[RotScaling] = None
@@ -113,7 +113,7 @@ class PaposunConfig:
                 mixer = GatedAttention(
                     heads=int(_need(m, "heads", mat)), kv_heads=int(_need(m, "kv_heads", mat)), dim=int(_need(m, "dim", mat)),
                     vdim=int(_need(m, "vdim", mat)), scale=float(_need(m, "scale", mat)),
-                    chunk=int(_need(_need(m, "mask", mat), "size", mat + "mask.")),
+                    chunk=int(_need(m["mask"], "size", mat + "mask.")) if m.get("mask") else None,
                     rot_dims=int(_need(rot, "dims", mat + "rot.")), rot_base=float(_need(rot, "base", mat + "rot.")),
                     rot_scaling=scaling, kv_from=None if kv_from is None else int(kv_from))
             elif kind == "mlstm":
@@ -154,7 +154,7 @@ class PaposunConfig:
             m = L.mixer
             at = f"layers[{i}].mixer"
             if isinstance(m, GatedAttention):
-                if min(m.heads, m.kv_heads, m.dim, m.vdim, m.chunk) < 1:
+                if min(m.heads, m.kv_heads, m.dim, m.vdim, m.chunk if m.chunk is not None else 1) < 1:
                     raise ConfigError(f"{at}: heads, kv_heads, dim, vdim and mask.size must be positive")
                 if m.heads % m.kv_heads:
                     raise ConfigError(f"{at}: {m.heads} heads are no multiple of {m.kv_heads} kv_heads")
@@ -189,8 +189,9 @@ class PaposunConfig:
                 if m.rot_scaling is not None:
                     s = m.rot_scaling
                     rot["scaling"] = {"factor": s.factor, "low": s.low, "high": s.high, "original": s.original}
-                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
-                         "mask": {"size": m.chunk}, "rot": rot}
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale, "rot": rot}
+                if m.chunk is not None:
+                    mixer["mask"] = {"size": m.chunk}
                 if m.kv_from is not None:
                     mixer["kv_from"] = m.kv_from
             else:
@@ -218,7 +219,7 @@ class PaposunConfig:
                     scaling = {"factor": s.factor, "low": s.low, "high": s.high, "original": s.original}
                 mixer = PartSpec("paged_attention", {
                     "hidden_size": c.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
-                    "value_dim": m.vdim, "softmax_scale": m.scale, "window": ("chunk", m.chunk),
+                    "value_dim": m.vdim, "softmax_scale": m.scale, "window": ("chunk", m.chunk) if m.chunk is not None else ("full", 0),
                     "position": PartSpec("rotary_halves", {"rotary_dim": m.rot_dims, "theta": m.rot_base, "scaling": scaling}),
                     "bias": True, "output_gate": True, "kv_shared": m.kv_from is not None})
                 order.append(LayerCall(i, i if m.kv_from is None else m.kv_from, m.kv_from is None))

@@ -85,10 +85,10 @@ def rotate(x, rot, start=0):
 
 
 def chunk_mask(T, size):
-    """[T, T] True where row i may see column j: j <= i and both in the same chunk of `size` positions."""
+    """[T, T] True where row i may see column j: j <= i and both in the same chunk of `size` positions (no size: j <= i)."""
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
-    return (j <= i) & (i // size == j // size)
+    return (j <= i) if size is None else (j <= i) & (i // size == j // size)
 
 
 def attention_keys_values(h, w, mx):
@@ -106,7 +106,7 @@ def gated_attention(h, w, mx, keys, values):
     T = h.shape[0]
     H, G, dim, vdim = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
     q = rotate((h @ w["q"].T + w["q.b"]).reshape(T, H, dim), mx["rot"])
-    see = chunk_mask(T, int(mx["mask"]["size"]))
+    see = chunk_mask(T, int(mx["mask"]["size"]) if mx.get("mask") else None)
     out = torch.zeros(T, H, vdim, dtype=h.dtype)
     for a in range(H):
         g = a // (H // G)
