@@ -181,7 +181,7 @@ SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
     if (p->q_col < 0 || p->k_col < 0 || p->v_col < 0 || p->i_col < 0 || p->f_col < 0) return SPITE_BAD_ARG;
     const long long need = (long long)p->heads * (2LL * p->dim + p->vdim + 2);
     if (p->stride < need) return SPITE_BAD_ARG;
-    if (p->dim > 256) return SPITE_UNSUPPORTED;
+    if (p->dim > 512) return SPITE_UNSUPPORTED;
     if (p->heads > 65535 || p->n_segments > 65535) return SPITE_UNSUPPORTED;
     if (p->n_segments == 0) return SPITE_OK;
     const long long col_blocks = (p->vdim + COLS_PER_BLOCK - 1) / COLS_PER_BLOCK;
@@ -191,6 +191,7 @@ SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
     if (p->dim <= 32) SPITE_LAUNCH(mlstm_scan_kernel<1>, grid, 128, 0, st, *p);
     else if (p->dim <= 64) SPITE_LAUNCH(mlstm_scan_kernel<2>, grid, 128, 0, st, *p);
     else if (p->dim <= 128) SPITE_LAUNCH(mlstm_scan_kernel<4>, grid, 128, 0, st, *p);
-    else SPITE_LAUNCH(mlstm_scan_kernel<8>, grid, 128, 0, st, *p);
+    else if (p->dim <= 256) SPITE_LAUNCH(mlstm_scan_kernel<8>, grid, 128, 0, st, *p);
+    else SPITE_LAUNCH(mlstm_scan_kernel<16>, grid, 128, 0, st, *p);
     return spite_launch_status();
 }

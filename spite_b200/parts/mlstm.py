@@ -38,8 +38,8 @@ class MatrixLstm(Mixer):
         self.d, self.H, self.kd, self.vd = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
         if min(self.d, self.H, self.kd, self.vd) < 1:
             raise ConfigError("mlstm: sizes must be positive")
-        if self.kd > 256:
-            raise ConfigError(f"mlstm: head_dim {self.kd} exceeds the scan kernel's 256")
+        if self.kd > 512:
+            raise ConfigError(f"mlstm: head_dim {self.kd} exceeds the scan kernel's 512")
         if not float(gate_cap) > 0 or not float(norm_eps) > 0:
             raise ConfigError("mlstm: gate_cap and norm_eps must be positive")
         self.cap, self.eps = float(gate_cap), float(norm_eps)

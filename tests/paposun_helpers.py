@@ -102,16 +102,29 @@ def folder_contents(folder: str):
 _plain_cache: dict = {}
 
 
-def plain_logits(folder, tokens):
-    """(logits computed in float64, what rounding to float32 alone moves every position by, as a fraction of the
-    largest logit).  A position at which a head of a memory puts out next to nothing, or n . q nearly cancels, is
-    ill-conditioned: there float32 itself is off by far more than elsewhere, and the comparison allows for it."""
-    key = (str(folder), tuple(tokens))
+def plain_logits(folder, tokens, sixteen=False):
+    """(logits computed in float64, what a position may be off by through rounding alone, as a fraction of the largest
+    logit).  For float32 arithmetic: four times the distance of a float32 run.  With `sixteen`, for activations kept in
+    bfloat16: in an otherwise float64 computation the inputs of every matrix product and attention's queries, keys,
+    values and heads are disturbed by random relative errors four times as large as a rounding to bfloat16 makes
+    (up to 2^-7); the largest distance among three draws counts, or four times the distance of a run that rounds these
+    to bfloat16 exactly as an engine would (which reproduces the turns of sign that the engine's own rounding causes).  A position at which a head of a memory puts out next
+    to nothing (its direction, which is all its norm keeps, then turns on the sign of q . k), or n . q nearly cancels,
+    is ill-conditioned: there rounding moves the logits by far more than elsewhere, out of proportion to its size, and
+    the comparison allows for it."""
+    key = (str(folder), tuple(tokens), sixteen)
     if key not in _plain_cache:
         cfg, tensors = folder_contents(str(folder))
         ref = plain.forward(cfg, tensors, list(tokens), torch.float64)
-        low = plain.forward(cfg, tensors, list(tokens), torch.float32).double()
-        _plain_cache[key] = (ref, (ref - low).abs().amax(-1) / float(ref.abs().max()))
+        if sixteen:
+            g = torch.Generator().manual_seed(len(tokens))
+            shake = lambda x: x * (1.0 + 2.0 ** -7 * (2.0 * torch.rand(x.shape, generator=g, dtype=x.dtype) - 1.0))
+            lows = [plain.forward(cfg, tensors, list(tokens), torch.float64, round_inputs=shake) for _ in range(3)]
+            exact = plain.forward(cfg, tensors, list(tokens), torch.float64, round_inputs=lambda x: x.to(torch.bfloat16).to(x.dtype))
+            moved = torch.stack([(ref - low).abs().amax(-1) for low in lows] + [4.0 * (ref - exact).abs().amax(-1)]).amax(0)
+        else:
+            moved = 4.0 * (ref - plain.forward(cfg, tensors, list(tokens), torch.float32).double()).abs().amax(-1)
+        _plain_cache[key] = (ref, moved / float(ref.abs().max()))
     return _plain_cache[key]
 
 
@@ -124,19 +137,33 @@ def generate_greedy(cfg, tensors, prompt, n):
 
 def compare_with_plain(results: dict, folder, requests: dict, tol: float):
     """Every logits row against the plain implementation in float64, as a fraction of the largest logit of the
-    sequence; a position may be off by `tol` or by four times what float32 rounding alone does to it, whichever is
-    more; names the first position beyond that."""
+    sequence; names the first position beyond its allowance.  In float32 a position may be off by `tol` or by what
+    `plain_logits` finds that rounding alone may do to it, whichever is more.  In the 16-bit comparison (a `tol` of a
+    thousandth or more) the positions that the disturbed runs move by more than twice `tol` are ill-conditioned and
+    left to the float32 comparison (they must stay a minority); of the others one in twenty-five of a request (or two) may
+    be off by up to four times their allowance: the estimate is four draws."""
     worst = 0.0
+    sixteen = tol >= 1e-3
+    judged = skipped = 0
     for r, toks in requests.items():
-        ref, rounding = plain_logits(folder, toks)
+        ref, rounding = plain_logits(folder, toks, sixteen=sixteen)
         scale = float(ref.abs().max())
+        spare = max(2, len(toks) // 25) if sixteen else 0
         for p in range(len(toks)):
             if (r, p) not in results:
                 continue
+            if sixteen and float(rounding[p]) > 2.0 * tol:
+                skipped += 1
+                continue
+            judged += 1
             err = float((results[(r, p)].double().cpu() - ref[p]).abs().max()) / scale
-            allowed = max(tol, 4.0 * float(rounding[p]))
+            allowed = max(tol, float(rounding[p]))
+            if allowed < err <= 4.0 * allowed and spare > 0:
+                spare -= 1
+                continue
             worst = max(worst, err * tol / allowed)
             assert err <= allowed, (f"request {r!r}, position {p} (first wrong one): error {err:.3e} of the "
                                     f"logit scale exceeds {allowed:.1e} (worst before it: {worst:.3e})")
+    assert judged >= skipped, f"{skipped} ill-conditioned positions beside {judged} others: this model tests little"
     note_error(worst, tol)
     return worst

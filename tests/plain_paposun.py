@@ -37,6 +37,13 @@ def load_folder(folder):
 
 
 # ---------------------------------------------------------------------------------- mechanisms
+_round = None        # `forward(round_inputs=...)`: applied to the activations that enter every matrix product and to what attention reads and writes
+
+
+def _in(x):
+    return x if _round is None else _round(x)
+
+
 def rms_norm(x, w, eps):
     """y = x / sqrt(mean(x^2) + eps) * w; the epsilon stands inside the root."""
     y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
@@ -94,18 +101,20 @@ def chunk_mask(T, size):
 def attention_keys_values(h, w, mx):
     """The layer's own rotated keys and its values: ([T, G, dim], [T, G, vdim])."""
     T = h.shape[0]
+    h = _in(h)
     G, dim, vdim = int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
     k = (h @ w["k"].T + w["k.b"]).reshape(T, G, dim)
     v = (h @ w["v"].T + w["v.b"]).reshape(T, G, vdim)
-    return rotate(k, mx["rot"]), v
+    return _in(rotate(k, mx["rot"])), _in(v)
 
 
 def gated_attention(h, w, mx, keys, values):
     """Grouped-query attention over the given (rotated) keys and values, softmax over the keys of the query's chunk,
     the concatenated heads times sigmoid(W_g h), then the output projection with its bias."""
     T = h.shape[0]
+    h = _in(h)
     H, G, dim, vdim = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
-    q = rotate((h @ w["q"].T + w["q.b"]).reshape(T, H, dim), mx["rot"])
+    q = _in(rotate((h @ w["q"].T + w["q.b"]).reshape(T, H, dim), mx["rot"]))
     see = chunk_mask(T, int(mx["mask"]["size"]) if mx.get("mask") else None)
     out = torch.zeros(T, H, vdim, dtype=h.dtype)
     for a in range(H):
@@ -114,7 +123,7 @@ def gated_attention(h, w, mx, keys, values):
         s = s.masked_fill(~see, -math.inf)
         out[:, a] = torch.softmax(s, -1) @ values[:, g]
     gate = torch.sigmoid(h @ w["g"].T)
-    return (out.reshape(T, H * vdim) * gate) @ w["o"].T + w["o.b"]
+    return _in(_in(out.reshape(T, H * vdim)) * gate) @ w["o"].T + w["o.b"]
 
 
 def mlstm(h, w, mx, eps):
@@ -124,6 +133,7 @@ def mlstm(h, w, mx, eps):
     o = S_t^T q / (max(|n_t . q|, e^(-m_t)) + 1e-6); every head's o over its root mean square, all heads times
     `norm`, times sigmoid(W_g h), then W_o."""
     T = h.shape[0]
+    h = _in(h)
     H, dim, vdim, cap = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"]), float(mx["gate_cap"])
     q = (h @ w["q"].T).reshape(T, H, dim) * dim ** -0.5
     k = (h @ w["k"].T).reshape(T, H, dim)
@@ -144,11 +154,11 @@ def mlstm(h, w, mx, eps):
             den = torch.maximum((n @ q[t, a]).abs(), torch.exp(-m)) + 1e-6
             out[t, a] = (S.T @ q[t, a]) / den
     out = rms_norm(out, None, eps).reshape(T, H * vdim) * w["norm"]
-    return (out * torch.sigmoid(h @ w["g"].T)) @ w["o"].T
+    return _in(out * torch.sigmoid(h @ w["g"].T)) @ w["o"].T
 
 
 def dense_ff(h, w):
-    return gelu_tanh(h @ w["up"].T) @ w["down"].T
+    return _in(gelu_tanh(_in(h) @ w["up"].T)) @ w["down"].T
 
 
 # ---------------------------------------------------------------------------------- the model
@@ -156,8 +166,20 @@ def _sub(tensors, prefix, dtype):
     return {k[len(prefix):]: v.to(dtype) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None):
-    """Logits [T, vocab] of one whole sequence.  `taps`, a list, receives the residual stream after every layer."""
+def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None, round_inputs=None):
+    """Logits [T, vocab] of one whole sequence.  `taps`, a list, receives the residual stream after every layer.
+    `round_inputs`, a function, is applied to the activations that enter every matrix product, to queries, keys and
+    values as attention reads them and to the heads it puts out (and to nothing else): with a rounding to 16 bits it
+    shows how far that rounding alone moves the logits."""
+    global _round
+    _round = round_inputs
+    try:
+        return _forward(cfg, tensors, tokens, dtype, taps)
+    finally:
+        _round = None
+
+
+def _forward(cfg, tensors, tokens, dtype, taps):
     eps, mult = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
     x = tensors["embed"].to(dtype)[torch.tensor(tokens, dtype=torch.long)]
     kept = {}                                           # layer -> its rotated keys and its values
@@ -183,5 +205,5 @@ def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None):
             x = x + mult * rms_norm(y, tensors[name + "norm2b"].to(dtype), eps)
         if taps is not None:
             taps.append(x.clone())
-    x = rms_norm(x, tensors["final.norm"].to(dtype), eps)
+    x = _in(rms_norm(x, tensors["final.norm"].to(dtype), eps))
     return (x @ tensors["embed"].to(dtype).T) * float(cfg["logit_scale"])
