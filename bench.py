@@ -13,6 +13,7 @@ Two further workloads print a line of the same kind (they are extra modes; the d
     python bench.py --config long        # Scout layer shapes, 8 layers: a prompt of 131,072 tokens in portions of
                                          # 8,192, then 256 decode steps at batch 1 and at batch 4
     python bench.py --config mibezen     # the Mibezen design beside Llama 4 at equal layer sizes, measured the same way
+    python bench.py --config paposun     # the Paposun design beside a dense Llama 4 at equal layer sizes, measured the same way
     python bench.py --config sezazen     # the Sezazen design beside Llama 4 at equal layer sizes (three sizes): prefill
                                          # of 2,048 tokens and decode at batch 1 and 8, each with its roofline fraction
 """
@@ -338,12 +339,37 @@ def mibezen_configs(size, runs=8):
     return mib, llama
 
 
+def paposun_configs(size, runs=8):
+    """A Paposun model of eight layers (a matrix memory without a feed-forward, an attention layer with a gelu feed-forward,
+    an attention layer that reads the one before's keys and values, and so on: three memories, five attention layers of
+    which two share) and a Llama 4 model of eight dense layers with the same width, heads, feed-forward width and
+    vocabulary.  A memory has 8 heads with width / 16 key rows and width / 8 value columns; a chunk is longer than the
+    measured contexts, so every earlier key is read."""
+    name, d, nq, nkv, kd, vd, E, top, f, fs, fd, V = size
+    rot = {"base": 500000.0, "dims": kd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    att = lambda src: dict({"heads": nq, "kv_heads": nkv, "dim": kd, "vdim": vd, "scale": kd ** -0.5, "mask": {"size": 8192}, "rot": rot},
+                           **({} if src is None else {"kv_from": src}))
+    mem = {"heads": 8, "dim": d // 16, "vdim": d // 8, "gate_cap": 15.0}
+    ff = {"kind": "dense", "ff": fd}
+    L = lambda t, m, mlp: {"type": t, "mixer": m, "mlp": mlp}
+    pap = {"architecture": "Paposun", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+           "logit_scale": 0.25,
+           "layers": [L("mlstm", mem, None), L("attention", att(None), ff), L("attention", att(1), ff), L("mlstm", mem, None),
+                      L("attention", att(None), ff), L("attention", att(4), ff), L("mlstm", mem, None), L("attention", att(None), ff)]}
+    llama = dict(SCOUT, num_hidden_layers=runs, hidden_size=d, num_attention_heads=nq, num_key_value_heads=nkv,
+                 head_dim=kd, num_local_experts=E, num_experts_per_tok=top, intermediate_size=f,
+                 intermediate_size_mlp=fd, moe_layers=[], vocab_size=V, tie_word_embeddings=True,
+                 max_position_embeddings=8192)
+    return pap, llama
+
+
 def design_work(model, T, contexts):
     """(flops of a prompt of T tokens, bytes a decode step over `contexts` must read), from the parts' own sizes
     as the design states them (no padding): every layer run reads its weights once; experts by the tokens' draw."""
     from spite_b200.config.specs import LayerCall
     from spite_b200.parts.feedforward import DenseActivation, MoESigmoidPrescaled, MoESoftmaxTopK
     from spite_b200.parts.latent import LatentAttention
+    from spite_b200.parts.mlstm import MatrixLstm
     es, p = 2, model.plan
     flops, nbytes = 2 * p.hidden_size * p.vocab_size, p.vocab_size * p.hidden_size * es
     for j in model.junctions:
@@ -360,8 +386,16 @@ def design_work(model, T, contexts):
             w = d * (m.rq + m.rkv + m.dr + m.nq) + m.rq * m.nq * (m.dn + m.dr) + m.nq * (m.dn + m.dv) * m.rkv + m.nq * m.dv * d
             flops += 2 * T * w + 2 * m.nq * (m.dn + m.dr + m.dv) * T * (T + 1) // 2
             nbytes += w * es + sum(c * (m.rkv + m.dr) * es for c in contexts)
+        elif isinstance(m, MatrixLstm):
+            # projections (q, k, v, the gate, the two gates of the recurrence) and the output; per token and head the
+            # state's update and its read-out, two multiply-adds an element; a decode step reads and writes the state
+            w = d * (2 * m.H * m.kd + 2 * m.H * m.vd + 2 * m.H) + m.H * m.vd * d
+            flops += 2 * T * w + 4 * T * m.H * m.kd * m.vd
+            nbytes += w * es + len(contexts) * 2 * m.H * (m.kd * m.vd + m.kd + 1) * 4
         else:
-            w = d * (m.nq * m.kd + m.nkv * m.kd + m.nkv * m.vd) + m.nq * m.vd * d + (m.nq * d if getattr(m, "head_gate", False) else 0)
+            shared = getattr(m, "kv_shared", False)
+            w = d * (m.nq * m.kd + (0 if shared else m.nkv * (m.kd + m.vd))) + m.nq * m.vd * d + \
+                (m.nq * d if getattr(m, "head_gate", False) else 0) + (m.nq * m.vd * d if getattr(m, "output_gate", False) else 0)
             flops += 2 * T * w + 2 * m.nq * (m.kd + m.vd) * T * (T + 1) // 2
             nbytes += w * es + sum(c * m.nkv * (m.kd + m.vd) * es for c in contexts)
         f = blk.ffn
@@ -392,12 +426,12 @@ def torch_unique(ffn):
 
 
 def run_sezazen(args):
-    """A design (`--config sezazen` or `mibezen`) beside the closest existing one, Llama 4, at equal layer sizes:
+    """A design (`--config sezazen`, `mibezen` or `paposun`) beside the closest existing one, Llama 4, at equal layer sizes:
     prefill of 2,048 tokens (a fraction of the sustained bf16 rate) and decode at batch 1 and 8 with 2,048 cached
     tokens (a fraction of the copy bandwidth).  One JSON line; `value` is the design's decode rate at batch 8 at
     the first size."""
     design = args.config
-    configs_of = design_configs if design == "sezazen" else mibezen_configs
+    configs_of = {"sezazen": design_configs, "mibezen": mibezen_configs, "paposun": paposun_configs}[design]
     import torch
     from spite_b200.config import config_from_dict
     from spite_b200.engine import Engine, Model, StepEntry
@@ -678,8 +712,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen", "mibezen"], default="scout",
-                    help="scout: the benchmark line; maverick, long, sezazen, mibezen: further workloads, one line each")
+    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen", "mibezen", "paposun"], default="scout",
+                    help="scout: the benchmark line; maverick, long, sezazen, mibezen, paposun: further workloads, one line each")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -689,8 +723,8 @@ def main(argv=None):
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
     ap.add_argument("--verbose", action="store_true", help="print the single prefill timings to standard error")
     ap.add_argument("--size", default=None, help="--config sezazen: only this set of layer sizes (small, medium, ...)")
-    ap.add_argument("--design", choices=["both", "sezazen", "mibezen", "llama4"], default="both",
-                    help="--config sezazen / mibezen: only this design")
+    ap.add_argument("--design", choices=["both", "sezazen", "mibezen", "paposun", "llama4"], default="both",
+                    help="--config sezazen / mibezen / paposun: only this design")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)
@@ -703,7 +737,7 @@ def main(argv=None):
     if args.config == "long":
         run_long(args)
         return 0
-    if args.config in ("sezazen", "mibezen"):
+    if args.config in ("sezazen", "mibezen", "paposun"):
         run_sezazen(args)
         return 0
     if args.warmup < 3:

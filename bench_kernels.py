@@ -12,10 +12,13 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py --only attention_decode,attention_prefill --latent   # ... over latent rows (one plane, 16 heads on one kv head)
     python bench_kernels.py --only gated_less    # experts without a gate (squared ReLU), the junction of a loop,
                                                  # the embedding with learned positions
+    python bench_kernels.py --only recurrent     # the matrix memory's scan in prompts and decode steps, the heads' norm
+                                                 # and gate, the norm behind a sublayer
 
 Families: gemm_decode (weight streaming, mma.sync), gemm_prefill (tcgen05/TMA),
 moe_decode, moe_prefill (grouped products), attention_decode, attention_prefill,
-small (norm, rotation + cache append, router, sampling), gated_less (what the Sezazen design adds).
+small (norm, rotation + cache append, router, sampling), gated_less (what the Sezazen design adds),
+recurrent (what the Paposun design adds).
 """
 from __future__ import annotations
 
@@ -298,6 +301,51 @@ def main(argv=None):
                                                  offsets_out=offs, sorted_out=qs)
             nbytes = M * lh * ((dn + dr) * 2 + (row - rkv) * 2 + dn * 2 + 4)
             report("latent", f"latent_queries M={M}", timed_rotating(make_queries, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+
+    # ---- the matrix memory's scan (8 heads of 256 key rows and 512 value columns, float32), the heads' norm with gain and
+    # gate behind it, and the norm that stands behind a sublayer
+    if want("recurrent"):
+        H, kd, vd, dm = (8, 128, 256, 2048) if args.small else (8, 256, 512, 4096)
+        size = ks.mlstm_state_size(kd, vd)
+        cols = (0, H * kd, 2 * H * kd, 2 * H * kd + 2 * H * vd, 2 * H * kd + 2 * H * vd + H)
+        width = -(-(cols[4] + H) // 8) * 8
+        fma_peak = 148 * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6            # float32 multiply-adds of the CUDA cores, FLOP/s
+        zero = torch.zeros(H, device=dev)
+        for n_seg, n_tok in ((1, 2048), (8, 2048), (1, 1), (8, 1), (64, 1)):
+            M = n_seg * n_tok
+            segs = [Segment(i, i, 0, n_tok, i * n_tok, True) for i in range(n_seg)]
+            batch = build_step_batch(segs, [[0] * n_tok] * n_seg, [[]] * n_seg, [[[0]] * n_seg], dev)
+            def make_scan(M=M, batch=batch, n_seg=n_seg):
+                proj = torch.randn((M, width), device=dev)
+                out = torch.empty((M, H * vd), device=dev)
+                state = torch.zeros((n_seg, H, size), device=dev)
+                return lambda: ks.mlstm_scan(proj, out, batch, state, heads=H, dim=kd, vdim=vd, gate_cap=15.0, q_scale=kd ** -0.5,
+                                             columns=cols, i_bias=zero, f_bias=zero)
+            nbytes = n_seg * H * size * 4 * 2 + M * (2 * H * kd + 2 * H * vd + 2 * H) * 4
+            flops = 4 * M * H * kd * vd
+            name = f"mlstm_scan {n_seg} x {n_tok} tokens, {H} heads of {kd} x {vd}"
+            if n_tok > 1:
+                timer = timed(make_scan())
+                if not (args.case and args.case not in name):
+                    ms = timer()
+                    print(json.dumps({"family": "recurrent", "case": name, "us": round(ms * 1e3, 2), "TFLOPs_fp32": round(flops / ms / 1e9, 2),
+                                      "fp32_fma_frac": round(flops / (ms * 1e-3) / fma_peak, 3), "GBps": round(nbytes / ms / 1e6, 1),
+                                      "peaks": src}), flush=True)
+            else:
+                report("recurrent", name, timed_rotating(make_scan, nbytes), nbytes=nbytes)
+        for M in (8, 2048):
+            def make_heads(M=M):
+                o, proj = torch.randn((M, H * vd), device=dev), torch.randn((M, width), device=dev)
+                a, gain = torch.empty((M, H * vd), dtype=bf, device=dev), torch.ones(H * vd, device=dev)
+                return lambda: ks.head_norm_gate(o, a, heads=H, size=vd, gates=proj, gate_column=cols[2] + H * vd, gain=gain, eps=1e-6)
+            nbytes = M * H * vd * (4 + 4 + 2)
+            report("recurrent", f"head_norm_gate M={M}, {H} heads of {vd}", timed_rotating(make_heads, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+            def make_join(M=M):
+                y, h, g1, g2 = torch.randn((M, dm), device=dev), torch.randn((M, dm), device=dev), torch.ones(dm, device=dev), torch.ones(dm, device=dev)
+                x = torch.empty((M, dm), dtype=bf, device=dev)
+                return lambda: ks.rms_norm_residual(y, g1, 1e-6, 0.3, h, next_gain=g2, next_out=x)
+            nbytes = M * dm * (4 + 4 + 4 + 2)
+            report("recurrent", f"rms_norm_residual with the next norm M={M} d={dm}", timed_rotating(make_join, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
 
     # ---- the small kernels of a decode step
     if want("small"):
