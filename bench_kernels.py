@@ -315,20 +315,22 @@ def main(argv=None):
             M = n_seg * n_tok
             segs = [Segment(i, i, 0, n_tok, i * n_tok, True) for i in range(n_seg)]
             batch = build_step_batch(segs, [[0] * n_tok] * n_seg, [[]] * n_seg, [[[0]] * n_seg], dev)
-            def make_scan(M=M, batch=batch, n_seg=n_seg):
+            def make_scan(M=M, batch=batch, n_seg=n_seg, chunked=False):
                 proj = torch.randn((M, width), device=dev)
                 out = torch.empty((M, H * vd), device=dev)
                 state = torch.zeros((n_seg, H, size), device=dev)
                 return lambda: ks.mlstm_scan(proj, out, batch, state, heads=H, dim=kd, vdim=vd, gate_cap=15.0, q_scale=kd ** -0.5,
-                                             columns=cols, i_bias=zero, f_bias=zero)
+                                             columns=cols, i_bias=zero, f_bias=zero, chunked=chunked)
             nbytes = n_seg * H * size * 4 * 2 + M * (2 * H * kd + 2 * H * vd + 2 * H) * 4
             flops = 4 * M * H * kd * vd
             name = f"mlstm_scan {n_seg} x {n_tok} tokens, {H} heads of {kd} x {vd}"
             if n_tok > 1:
-                timer = timed(make_scan())
-                if not (args.case and args.case not in name):
-                    ms = timer()
-                    print(json.dumps({"family": "recurrent", "case": name, "us": round(ms * 1e3, 2), "TFLOPs_fp32": round(flops / ms / 1e9, 2),
+                for chunked in (False, True):
+                    full = name + (", 32 tokens at a time" if chunked else ", token by token")
+                    if args.case and args.case not in full:
+                        continue
+                    ms = timed(make_scan(chunked=chunked))()
+                    print(json.dumps({"family": "recurrent", "case": full, "us": round(ms * 1e3, 2), "TFLOPs_fp32": round(flops / ms / 1e9, 2),
                                       "fp32_fma_frac": round(flops / (ms * 1e-3) / fma_peak, 3), "GBps": round(nbytes / ms / 1e6, 1),
                                       "peaks": src}), flush=True)
             else:

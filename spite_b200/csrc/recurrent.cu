@@ -32,6 +32,7 @@ struct MlstmParams {
     const int* slots;           // [segments]: the state slot of a segment's request
     int n_segments, heads, dim, vdim;
     float gate_cap, q_scale;
+    int chunked;                // not 0: segments are walked 32 tokens at a time (prompts and their portions)
 };
 
 namespace {
@@ -172,6 +173,342 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmParams p) {
     if (warp == 0 && lane == 0) st_n[dim] = m;
 }
 
+// ---- the same recurrence, 32 tokens at a time (prompts and their portions).
+// With F_t the sum of the log forget gates from the chunk's first token to t, a_s = i_s - F_s, m0 the maximum the chunk
+// starts from and M_t = max(m0, max_{s<=t} a_s), the recurrence unrolls to m_t = F_t + M_t and
+//     S_t = exp(m0 - M_t) S_0 + sum_{s<=t} exp(a_s - M_t) k_s v_s^T                 (n_t alike)
+// so a chunk is three small matrix products in float32 on the CUDA cores, none of which waits for a token before it:
+//     [q S_0 | q n_0 | q k^T]   (tokens x (32 value columns, 1, 32 keys), over the key rows),
+//     numerators = exp(m0 - M_t) q S_0 + sum_{s<=t} exp(a_s - M_t) (q_t . k_s) v_s   (the denominator's n . q alike),
+//     S <- exp(m0 - M_last) S + sum_s exp(a_s - M_last) k_s v_s^T.
+// Every exponent is <= 0.  A block owns 32 value columns of one (segment, head), as in the kernel above, with the
+// state tile, the chunk's q, k and v in shared memory; 256 threads.
+constexpr int CL = 32;            // tokens of a chunk
+constexpr int SROW = 36;          // floats of a row of the state tile: 32 value columns, n, three zeros
+
+template <int RPL2> struct ChunkSmem {
+    static constexpr int DP = 64 * RPL2;          // key rows, padded with zeros
+    static constexpr int FLOATS = DP * SROW + 2 * CL * DP + 3 * CL * CL + 7 * CL + 4;      // (two of the small arrays hold doubles)
+    // 115,600 bytes at 256 key rows: two blocks fit a multiprocessor
+};
+
+__device__ __forceinline__ double warp_prefix_sum(double v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+    }
+    return v;
+}
+__device__ __forceinline__ double warp_prefix_max(double v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v = fmax(v, u);
+    }
+    return v;
+}
+
+__device__ __forceinline__ void copy16_async(void* smem, const void* gmem, int src_bytes) {     // the rest of the 16 bytes: zeros
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+template <int RPL2>
+__global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(const MlstmParams p) {
+    constexpr int DP = ChunkSmem<RPL2>::DP;
+    extern __shared__ __align__(16) float sm[];
+    float* S_s = sm;                              // [DP][SROW]: the state's 32 columns, then n
+    // [CL][DP]; element d of token t lies at d ^ 4 (t & 7), so that the rows of eight tokens in a row, read four
+    // floats at a time at the same d, fall on different banks
+    float* q_s = S_s + DP * SROW;                 // (not yet scaled: q_scale multiplies the sums)
+    float* k_s = q_s + CL * DP;                   // [CL][DP]
+    float* v_s = k_s + CL * DP;                 // [CL][32]: the block's value columns
+    float* X0 = v_s + CL * CL;                    // [CL][32]: q S_0, first half the sums, then scaled by exp(m0 - M_t)
+    float* X1 = X0 + CL * CL;                     // [CL][CL]: q k^T, first half the sums, then weighted and masked
+    // a_s and M_t as doubles: they are differences of sums over the chunk's gates, and exp(a_s - M_t) is to be as exact
+    // as exp of a single gate in the walk token by token, also where the gates are large
+    double* g_a = reinterpret_cast<double*>(X1 + CL * CL);
+    double* g_M = g_a + CL;
+    float* g_m = reinterpret_cast<float*>(g_M + CL);       // [CL] each: m_t, exp(m0 - M_t), exp(a_s - M_last)
+    float* g_g = g_m + CL;
+    float* g_w = g_g + CL;
+    float* g_last_s = g_w + CL;                   // [1]: exp(m0 - M_last)
+
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seg = blockIdx.z, head = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cb0 = blockIdx.x * 32;
+    const int t0 = p.cu_seqlens[seg], t1 = p.cu_seqlens[seg + 1];
+    const int dim = p.dim, vdim = p.vdim;
+    if (t0 >= t1) return;
+    const int slot = p.slots[seg];
+    const size_t out_stride = (size_t)p.heads * vdim;
+    if (seg > 0 && slot == p.slots[0]) {          // a padding row of a captured step (see the kernel above)
+        for (int e = tid; e < (t1 - t0) * 32; e += 256)
+            if (cb0 + (e & 31) < vdim) p.out[(size_t)(t0 + (e >> 5)) * out_stride + (size_t)head * vdim + cb0 + (e & 31)] = 0.f;
+        return;
+    }
+    float* st = p.state + ((size_t)slot * p.heads + head) * (size_t)p.head_stride;
+    float* st_n = st + (size_t)dim * vdim + (size_t)blockIdx.x * ((dim + 1 + 3) & ~3);
+    for (int e = tid; e < DP * SROW; e += 256) {
+        const int d = e / SROW, c = e - d * SROW;
+        float x = 0.f;
+        if (d < dim) {
+            if (c < 32) { if (cb0 + c < vdim) x = st[(size_t)d * vdim + cb0 + c]; }
+            else if (c == 32) x = st_n[d];
+        }
+        S_s[e] = x;
+    }
+    float m_run = st_n[dim];
+    const float bi = p.i_bias ? p.i_bias[head] : 0.f, bf = p.f_bias ? p.f_bias[head] : 0.f;
+    const float cap = p.gate_cap, inv_cap = 1.0f / p.gate_cap;
+    // q and k rows move as groups of four floats where every such group is aligned
+    const bool vec4 = (dim % 4) == 0 && (p.stride % 4) == 0 && (p.q_col % 4) == 0 && (p.k_col % 4) == 0 && (((uintptr_t)p.proj) & 15) == 0;
+
+    // The next chunk's inputs are asked for while the current one is worked on: q and k by asynchronous copies of 16
+    // bytes straight into shared memory (q once the products that read it are done, k once the state is renewed), the
+    // 32 x 32 values and the gates into registers.  Rows that are not 16-byte aligned are loaded at the chunk's start.
+    auto fetch_rows = [&](int c, int col, float* dst, bool swizzle) {
+        if (!vec4 || c >= t1) return;
+        const float* rows = p.proj + (size_t)c * p.stride + col + head * dim;
+        const int len = min(CL, t1 - c);
+#pragma unroll 4
+        for (int e = tid; e < CL * (DP / 4); e += 256) {
+            const int t = e / (DP / 4), d = (e - t * (DP / 4)) * 4;
+            const bool on = t < len && d < dim;
+            copy16_async(&dst[t * DP + (swizzle ? (d ^ ((t & 7) << 2)) : d)], on ? (const void*)&rows[(size_t)t * p.stride + d] : (const void*)p.proj, on ? 16 : 0);
+        }
+        copy_async_commit();
+    };
+    float v_next[4], gi_next = 0.f, gf_next = 0.f;
+    auto fetch_small = [&](int c) {
+        if (c >= t1) return;
+        const float* rows = p.proj + (size_t)c * p.stride;
+        const int len = min(CL, t1 - c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = tid + 256 * i, t = e >> 5, cc = e & 31;
+            v_next[i] = (t < len && cb0 + cc < vdim) ? rows[(size_t)t * p.stride + p.v_col + head * vdim + cb0 + cc] : 0.f;
+        }
+        if (warp == 0 && lane < len) {
+            gi_next = rows[(size_t)lane * p.stride + p.i_col + head];
+            gf_next = rows[(size_t)lane * p.stride + p.f_col + head];
+        }
+    };
+    fetch_rows(t0, p.q_col, q_s, true);
+    fetch_rows(t0, p.k_col, k_s, false);
+    fetch_small(t0);
+
+    for (int c0 = t0; c0 < t1; c0 += CL) {
+        const int len = min(CL, t1 - c0);
+        // ---- the chunk's q, k and v are in place; the gates and what follows from them (warp 0, a lane a token)
+        if (vec4) copy_async_wait_all();
+        else {
+            const float* rows = p.proj + (size_t)c0 * p.stride;
+            for (int e = tid; e < CL * DP; e += 256) {
+                const int t = e / DP, d = e - t * DP;
+                const bool on = t < len && d < dim;
+                q_s[t * DP + (d ^ ((t & 7) << 2))] = on ? rows[(size_t)t * p.stride + p.q_col + head * dim + d] : 0.f;
+                k_s[t * DP + d] = on ? rows[(size_t)t * p.stride + p.k_col + head * dim + d] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v_s[tid + 256 * i] = v_next[i];
+        if (warp == 0) {
+            const bool on = lane < len;
+            float ig = 0.f, fg = 0.f;
+            if (on) {
+                ig = cap * tanhf((gi_next + bi) * inv_cap);
+                fg = log_sigmoid(cap * tanhf((gf_next + bf) * inv_cap));
+            }
+            const double F = warp_prefix_sum((double)fg, lane);
+            const double a = on ? (double)ig - F : -1.0e300;
+            const double M = fmax((double)m_run, warp_prefix_max(a, lane));
+            const double M_last = __shfl_sync(0xffffffffu, M, len - 1), F_last = __shfl_sync(0xffffffffu, F, len - 1);
+            g_a[lane] = a;
+            g_M[lane] = M;
+            g_m[lane] = (float)(F + M);
+            g_g[lane] = expf((float)((double)m_run - M));
+            // The maximum goes on as a float.  The state is scaled to that rounded value, not to the sum it was rounded
+            // from, so that state and maximum agree exactly, as they do in the walk token by token.
+            const float m_next = (float)(F_last + M_last);
+            const double M_state = (double)m_next - F_last;
+            g_w[lane] = on ? expf((float)(a - M_state)) : 0.f;
+            if (lane == 0) g_last_s[0] = expf((float)((double)m_run - M_state));
+            m_run = m_next;
+        }
+        __syncthreads();
+
+        // ---- [q S_0 | q k^T]: a thread has 4 tokens (tg, tg + 8, ...) by 4 columns, over half of the key rows
+        const int kh = tid >> 7, w4 = warp & 3, tg = lane & 7, cg = (lane >> 3) + 4 * (w4 & 1);
+        const bool keys = w4 >= 2;
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        {
+            const int d_lo = kh * (DP / 2), d_hi = d_lo + DP / 2;
+            if (!keys) {
+                for (int d = d_lo; d < d_hi; d += 4) {
+                    float4 qv[4], sv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) qv[i] = *(const float4*)&q_s[(tg + 8 * i) * DP + (d ^ (tg << 2))];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sv[e] = *(const float4*)&S_s[(d + e) * SROW + 4 * cg];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float qe[4] = {qv[i].x, qv[i].y, qv[i].z, qv[i].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[i][0] = fmaf(qe[e], sv[e].x, acc[i][0]);
+                            acc[i][1] = fmaf(qe[e], sv[e].y, acc[i][1]);
+                            acc[i][2] = fmaf(qe[e], sv[e].z, acc[i][2]);
+                            acc[i][3] = fmaf(qe[e], sv[e].w, acc[i][3]);
+                        }
+                    }
+                }
+            } else {
+                for (int d = d_lo; d < d_hi; d += 4) {
+                    float4 qv[4], kv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) qv[i] = *(const float4*)&q_s[(tg + 8 * i) * DP + (d ^ (tg << 2))];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) kv[j] = *(const float4*)&k_s[(4 * cg + j) * DP + d];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[i][j] = fmaf(qv[i].x, kv[j].x, acc[i][j]);
+                            acc[i][j] = fmaf(qv[i].y, kv[j].y, acc[i][j]);
+                            acc[i][j] = fmaf(qv[i].z, kv[j].z, acc[i][j]);
+                            acc[i][j] = fmaf(qv[i].w, kv[j].w, acc[i][j]);
+                        }
+                }
+            }
+        }
+        float* X = keys ? X1 : X0;
+        if (kh == 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *(float4*)&X[(tg + 8 * i) * CL + 4 * cg] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        }
+        // q . n_0 for token tid / 8: each of its 8 threads sums an eighth of the key rows (the same threads write the token's outputs)
+        float nq0 = 0.f;
+        for (int d = tid & 7; d < DP; d += 8) nq0 = fmaf(q_s[(tid >> 3) * DP + (d ^ (((tid >> 3) & 7) << 2))], S_s[d * SROW + 32], nq0);
+        nq0 += __shfl_xor_sync(0xffffffffu, nq0, 1);
+        nq0 += __shfl_xor_sync(0xffffffffu, nq0, 2);
+        nq0 += __shfl_xor_sync(0xffffffffu, nq0, 4);
+        __syncthreads();
+        fetch_rows(c0 + CL, p.q_col, q_s, true);      // (nothing reads this chunk's q any more)
+        fetch_small(c0 + CL);
+        if (kh == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int t = tg + 8 * i;
+                const float4 o = *(const float4*)&X[t * CL + 4 * cg];
+                float r[4] = {acc[i][0] + o.x, acc[i][1] + o.y, acc[i][2] + o.z, acc[i][3] + o.w};
+                if (!keys) {
+                    const float g = g_g[t] * p.q_scale;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) r[j] *= g;
+                } else {
+                    const double M = g_M[t];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int s = 4 * cg + j;
+                        r[j] = (s <= t && s < len) ? expf((float)(g_a[s] - M)) * (r[j] * p.q_scale) : 0.f;
+                    }
+                }
+                *(float4*)&X[t * CL + 4 * cg] = make_float4(r[0], r[1], r[2], r[3]);
+            }
+        }
+
+        // ---- the state after the chunk: a warp has 8 columns (warps 0..3 and 4..7: the two halves of the key rows),
+        // a lane the rows lane, lane + 32, ...; the warps of the first columns also renew n
+        {
+            const int cu0 = 8 * (warp & 3), d0 = (warp >> 2) * (DP / 2) + lane;
+            const bool with_n = (warp & 3) == 0;
+            const float g_last = g_last_s[0];
+            float a[RPL2][8], an[RPL2];
+#pragma unroll
+            for (int r = 0; r < RPL2; ++r) {
+                const float* row = &S_s[(d0 + 32 * r) * SROW];
+                const float4 x = *(const float4*)&row[cu0], y = *(const float4*)&row[cu0 + 4];
+                a[r][0] = g_last * x.x; a[r][1] = g_last * x.y; a[r][2] = g_last * x.z; a[r][3] = g_last * x.w;
+                a[r][4] = g_last * y.x; a[r][5] = g_last * y.y; a[r][6] = g_last * y.z; a[r][7] = g_last * y.w;
+                an[r] = g_last * row[32];
+            }
+            for (int s = 0; s < len; ++s) {
+                const float ws = g_w[s];
+                const float4 x = *(const float4*)&v_s[s * CL + cu0], y = *(const float4*)&v_s[s * CL + cu0 + 4];
+                const float vw[8] = {ws * x.x, ws * x.y, ws * x.z, ws * x.w, ws * y.x, ws * y.y, ws * y.z, ws * y.w};
+#pragma unroll
+                for (int r = 0; r < RPL2; ++r) {
+                    const float kv = k_s[s * DP + d0 + 32 * r];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a[r][j] = fmaf(kv, vw[j], a[r][j]);
+                    an[r] = fmaf(kv, ws, an[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RPL2; ++r) {
+                float* row = &S_s[(d0 + 32 * r) * SROW];
+                *(float4*)&row[cu0] = make_float4(a[r][0], a[r][1], a[r][2], a[r][3]);
+                *(float4*)&row[cu0 + 4] = make_float4(a[r][4], a[r][5], a[r][6], a[r][7]);
+                if (with_n) row[32] = an[r];
+            }
+        }
+        __syncthreads();
+        fetch_rows(c0 + CL, p.k_col, k_s, false);      // (the state is renewed: nothing reads this chunk's k any more)
+
+        // ---- the outputs: a thread has one token and 4 value columns
+        {
+            const int t = tid >> 3, cc = (tid & 7) * 4;
+            if (t < len) {
+                float nq = nq0 * (g_g[t] * p.q_scale);
+                float4 o = *(const float4*)&X0[t * CL + cc];
+                for (int s = 0; s <= t; ++s) {
+                    const float pw = X1[t * CL + s];
+                    const float4 vv = *(const float4*)&v_s[s * CL + cc];
+                    o.x = fmaf(pw, vv.x, o.x); o.y = fmaf(pw, vv.y, o.y); o.z = fmaf(pw, vv.z, o.z); o.w = fmaf(pw, vv.w, o.w);
+                    nq += pw;
+                }
+                const float den = fmaxf(fabsf(nq), expf(-g_m[t])) + 1e-6f;
+                float* dst = p.out + (size_t)(c0 + t) * out_stride + (size_t)head * vdim + cb0 + cc;
+                const float r[4] = {o.x / den, o.y / den, o.z / den, o.w / den};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (cb0 + cc + j < vdim) dst[j] = r[j];
+            }
+        }
+
+        __syncthreads();
+    }
+
+    for (int e = tid; e < DP * SROW; e += 256) {
+        const int d = e / SROW, c = e - d * SROW;
+        if (d >= dim) continue;
+        if (c < 32) { if (cb0 + c < vdim) st[(size_t)d * vdim + cb0 + c] = S_s[e]; }
+        else if (c == 32) st_n[d] = S_s[e];
+    }
+    if (tid == 0) st_n[dim] = m_run;
+}
+
+template <int RPL2>
+int launch_mlstm_chunk(const MlstmParams& p, dim3 grid, cudaStream_t st) {
+    const size_t smem = (size_t)ChunkSmem<RPL2>::FLOATS * sizeof(float);
+    auto k = mlstm_chunk_kernel<RPL2>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        return SPITE_LAUNCH_FAILED;
+    SPITE_LAUNCH(k, grid, 256, smem, st, p);
+    return spite_launch_status();
+}
+
 }  // namespace
 
 SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
@@ -188,6 +525,12 @@ SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
     if (p->head_stride < (long long)p->dim * p->vdim + col_blocks * ((p->dim + 1 + 3) & ~3)) return SPITE_BAD_ARG;
     dim3 grid((p->vdim + COLS_PER_BLOCK - 1) / COLS_PER_BLOCK, p->heads, p->n_segments);
     cudaStream_t st = (cudaStream_t)stream;
+    if (p->chunked) {
+        if (p->dim <= 64) return launch_mlstm_chunk<1>(*p, grid, st);
+        if (p->dim <= 128) return launch_mlstm_chunk<2>(*p, grid, st);
+        if (p->dim <= 256) return launch_mlstm_chunk<4>(*p, grid, st);
+        return launch_mlstm_chunk<8>(*p, grid, st);
+    }
     if (p->dim <= 32) SPITE_LAUNCH(mlstm_scan_kernel<1>, grid, 128, 0, st, *p);
     else if (p->dim <= 64) SPITE_LAUNCH(mlstm_scan_kernel<2>, grid, 128, 0, st, *p);
     else if (p->dim <= 128) SPITE_LAUNCH(mlstm_scan_kernel<4>, grid, 128, 0, st, *p);

@@ -178,7 +178,8 @@ class KernelSet:
         raise NotImplementedError
 
     # ---- recurrent mixers
-    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias,
+                   chunked=None):
         """Matrix memory with exponential gates, token by token, for every segment of the step from the state its
         request's slot holds (all zeros: the start of a sequence); the slot receives the state after the segment's
         last token.  proj float32 [M, *] holds, from the columns `columns` = (q, k, v, i, f) on, q and k
@@ -186,7 +187,8 @@ class KernelSet:
         state float32 [slots, heads, `mlstm_state_size(dim, vdim)`].
         i = cap tanh((a + i_bias) / cap), f = logsigmoid(cap tanh((c + f_bias) / cap)), m' = max(f + m, i),
         S' = exp(f + m - m') S + exp(i - m') k v^T, n' alike with k, out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6),
-        q times `q_scale`.  All float32."""
+        q times `q_scale`.  All float32.  `chunked`: walk the segments 32 tokens at a time (the same sums in another
+        order) instead of token by token; None leaves the choice to the kernel set."""
         raise NotImplementedError
 
     @staticmethod

@@ -83,7 +83,7 @@ class MlstmParams(C.Structure):
                 ("i_bias", C.c_void_p), ("f_bias", C.c_void_p), ("out", C.c_void_p), ("state", C.c_void_p),
                 ("head_stride", C.c_longlong), ("cu_seqlens", C.c_void_p), ("slots", C.c_void_p),
                 ("n_segments", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
-                ("gate_cap", C.c_float), ("q_scale", C.c_float)]
+                ("gate_cap", C.c_float), ("q_scale", C.c_float), ("chunked", C.c_int)]
 
 
 class AttnMmaExtra(C.Structure):
@@ -909,7 +909,8 @@ class CudaKernels(KernelSet):
         _check(st, "latent_queries")
 
     # ------------------------------------------------------------------ recurrent mixers
-    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias,
+                   chunked=None):
         self._t(proj, torch.float32, "proj"); self._t(out, torch.float32, "out"); self._t(state, torch.float32, "state")
         self._t(i_bias, torch.float32, "i_bias"); self._t(f_bias, torch.float32, "f_bias")
         M = proj.shape[0]
@@ -920,11 +921,15 @@ class CudaKernels(KernelSet):
         if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim, i_col + heads, f_col + heads) > proj.shape[1]:
             raise KernelError("mlstm_scan: the columns lie outside the projection's rows")
         n_seg = batch.cu_seqlens.numel() - 1
+        if chunked is None:
+            # Prompts and their portions go 32 tokens at a time.  The float32 set keeps the walk token by token for
+            # every step, so that its results do not depend on how a prompt was cut, to the last bit.
+            chunked = self.dtype != torch.float32 and batch.max_seg_len >= 8
         p = MlstmParams(proj=proj.data_ptr(), stride=proj.shape[1], q_col=q_col, k_col=k_col, v_col=v_col, i_col=i_col,
                         f_col=f_col, i_bias=i_bias.data_ptr(), f_bias=f_bias.data_ptr(), out=out.data_ptr(),
                         state=state.data_ptr(), head_stride=state.shape[2], cu_seqlens=batch.cu_seqlens.data_ptr(),
                         slots=batch.slots.data_ptr(), n_segments=n_seg, heads=int(heads), dim=int(dim), vdim=int(vdim),
-                        gate_cap=float(gate_cap), q_scale=float(q_scale))
+                        gate_cap=float(gate_cap), q_scale=float(q_scale), chunked=int(bool(chunked)))
         st = self._lib("recurrent").spite_mlstm_scan(C.byref(p), self._stream())
         self._count("recurrent", 1)
         _check(st, "mlstm_scan")

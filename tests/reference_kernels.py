@@ -76,7 +76,7 @@ class TorchReferenceKernels(KernelSet):
         out.copy_(v.to(out.dtype))
 
     # ---- recurrent mixers
-    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias):
+    def mlstm_scan(self, proj, out, batch, state, *, heads, dim, vdim, gate_cap, q_scale, columns, i_bias, f_bias, chunked=None):
         qc, kc, vc, ic, fc = columns
         x = proj.to(self.acc)
         cu = batch.cu_seqlens.tolist()

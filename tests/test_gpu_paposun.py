@@ -60,13 +60,17 @@ SCAN_CASES = [
     (2, 256, 40, 8.0, 1.0, 2.0, [(9, 1, 1)]),
     (4, 8, 8, 2.0, 0.01, 1.0, [(30, 1, 1), (1, 1, 1)]),         # tiny queries: the denominator is exp(-m), so the maximum's start at 0 shows
     (1, 300, 24, 6.0, 1.0, 2.0, [(7, 1, 3)]),
+    (2, 72, 36, 12.0, 1.0, 3.0, [(32, 33, 64), (97, 1, 31), (1, 65, 2)]),     # portions that end on, before and behind the edges of groups of 32 tokens
+    (1, 512, 33, 9.0, 1.0, 2.0, [(34, 3, 1)]),
 ]
 
 
+@pytest.mark.parametrize("chunked", [False, True], ids=["token by token", "32 tokens at a time"])
 @pytest.mark.parametrize("case", range(len(SCAN_CASES)))
-def test_memory_scan_in_prompts_portions_and_decoded_tokens(case):
+def test_memory_scan_in_prompts_portions_and_decoded_tokens(case, chunked):
     """Three steps over the same slots: every segment goes on from the state the step before left, slots are dealt out
-    of order, one slot holds another request's leftovers before it is cleared and taken.  Against float64 loops."""
+    of order, one slot holds another request's leftovers before it is cleared and taken.  Against float64 loops, with
+    the kernel that walks token by token and with the one that takes 32 tokens at a time."""
     heads, dim, vdim, cap, q_size, gate_size, segs = SCAN_CASES[case]
     ks = kernels(torch.float32)
     n_slots = len(segs) + 2
@@ -100,7 +104,7 @@ def test_memory_scan_in_prompts_portions_and_decoded_tokens(case):
             proj[3, cols[3]:cols[3] + heads] = 40.0           # one token is taken in far more strongly than the rest: it stays in the memory
         out = torch.empty((M, heads * vdim), dtype=torch.float32, device=DEV)
         ks.mlstm_scan(proj.to(DEV), out, batch, state, heads=heads, dim=dim, vdim=vdim, gate_cap=cap, q_scale=q_scale,
-                      columns=cols, i_bias=bi.to(DEV), f_bias=bf.to(DEV))
+                      columns=cols, i_bias=bi.to(DEV), f_bias=bf.to(DEV), chunked=chunked)
         torch.cuda.synchronize()
         assert not ks.errors()
         ref = torch.zeros(M, heads, vdim, dtype=torch.float64)
@@ -116,7 +120,8 @@ def test_memory_scan_in_prompts_portions_and_decoded_tokens(case):
                 carried[s][a] = (S1, n1, m1)
                 ref[off:off + n, a] = o
             off += n
-        close(out.view(M, heads, vdim), ref, 2e-5, f"memory scan, step {step}")
+        # 32 tokens at a time the same terms are summed in another order, more of them in one sum
+        close(out.view(M, heads, vdim), ref, 5e-5 if chunked else 2e-5, f"memory scan, step {step}")
     for s in range(len(segs)):                                # the state itself, as the slot holds it
         for a in range(heads):
             S1, n1, m1 = carried[s][a]
@@ -132,7 +137,8 @@ def test_memory_scan_in_prompts_portions_and_decoded_tokens(case):
 
 def test_memory_keeps_a_token_from_hundreds_of_steps_back():
     """Forget gates near one (log f near 0) and one token taken in strongly at position 2: after 700 more tokens, a
-    query aligned with that token's key still reads that token's value, in one prompt and decoded one by one."""
+    query aligned with that token's key still reads that token's value: in one prompt (token by token, and 32 tokens at
+    a time), decoded one by one, and in portions of many sizes."""
     ks = kernels(torch.float32)
     heads, dim, vdim, cap, T = 2, 48, 40, 15.0, 703
     from spite_b200.engine.batch import Segment, build_step_batch
@@ -146,14 +152,15 @@ def test_memory_keeps_a_token_from_hundreds_of_steps_back():
     zero = torch.zeros(heads, device=DEV)
     size = ks.mlstm_state_size(dim, vdim)
     outs = []
-    for counts in ([T], [3] + [1] * (T - 3)):
+    for counts, chunked in (([T], False), ([3] + [1] * (T - 3), False), ([T], True), ([31, 33, 64, 1, 2, 200, 9, 300, 63], True)):
+        assert sum(counts) == T
         state = torch.zeros((1, heads, size), device=DEV)
         got, at = [], 0
         for i, n in enumerate(counts):
             batch = build_step_batch([Segment(0, 0, at, n, 0, i == 0)], [[0] * n], [[]], [[[0]]], DEV)
             out = torch.empty((n, heads * vdim), dtype=torch.float32, device=DEV)
             ks.mlstm_scan(proj[at:at + n].contiguous().to(DEV), out, batch, state, heads=heads, dim=dim, vdim=vdim, gate_cap=cap,
-                          q_scale=dim ** -0.5, columns=cols, i_bias=zero, f_bias=zero)
+                          q_scale=dim ** -0.5, columns=cols, i_bias=zero, f_bias=zero, chunked=chunked)
             got.append(out.cpu())
             at += n
         outs.append(torch.cat(got))
@@ -164,6 +171,16 @@ def test_memory_keeps_a_token_from_hundreds_of_steps_back():
             cos = float(torch.nn.functional.cosine_similarity(last[a], v2, dim=0))
             assert cos > 0.95, cos
     close(outs[1], outs[0], 1e-5, "decoded against the prompt")
+    # Seven hundred decays near one, each rounded to float32: the walk token by token itself stands a few 1e-4 from the
+    # same loops in float64, and the other order of the sums may differ from it by as much.
+    ref = torch.zeros(T, heads, vdim, dtype=torch.float64)
+    pd = proj.double()
+    for a in range(heads):
+        ref[:, a] = memory_loops(pd[:, a * dim:(a + 1) * dim], pd[:, cols[1] + a * dim:cols[1] + (a + 1) * dim],
+                                 pd[:, cols[2] + a * vdim:cols[2] + (a + 1) * vdim], pd[:, cols[3] + a], pd[:, cols[4] + a], 0.0, 0.0, cap,
+                                 dim ** -0.5, torch.zeros(dim, vdim, dtype=torch.float64), torch.zeros(dim, dtype=torch.float64), 0.0)[0]
+    for out in outs:
+        close(out.view(T, heads, vdim), ref, 1e-3, "against loops in float64")
 
 
 # ---------------------------------------------------------------------------- between the heads and the output projection
