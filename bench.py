@@ -349,11 +349,11 @@ def paposun_configs(size, runs=8):
     rot = {"base": 500000.0, "dims": kd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     att = lambda src: dict({"heads": nq, "kv_heads": nkv, "dim": kd, "vdim": vd, "scale": kd ** -0.5, "mask": {"size": 8192}, "rot": rot},
                            **({} if src is None else {"kv_from": src}))
-    mem = {"heads": 8, "dim": d // 16, "vdim": d // 8, "gate_cap": 15.0}
+    mem = {"heads": 8, "dim": d // 16, "vdim": d // 8, "gate_cap": 10.0}
     ff = {"kind": "dense", "ff": fd}
     L = lambda t, m, mlp: {"type": t, "mixer": m, "mlp": mlp}
-    pap = {"architecture": "Paposun", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
-           "logit_scale": 0.25,
+    pap = {"architecture": "Paposun", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+           "logit_scale": 0.5,
            "layers": [L("mlstm", mem, None), L("attention", att(None), ff), L("attention", att(1), ff), L("mlstm", mem, None),
                       L("attention", att(None), ff), L("attention", att(4), ff), L("mlstm", mem, None), L("attention", att(None), ff)]}
     llama = dict(SCOUT, num_hidden_layers=runs, hidden_size=d, num_attention_heads=nq, num_key_value_heads=nkv,

@@ -319,7 +319,7 @@ def main(argv=None):
                 proj = torch.randn((M, width), device=dev)
                 out = torch.empty((M, H * vd), device=dev)
                 state = torch.zeros((n_seg, H, size), device=dev)
-                return lambda: ks.mlstm_scan(proj, out, batch, state, heads=H, dim=kd, vdim=vd, gate_cap=15.0, q_scale=kd ** -0.5,
+                return lambda: ks.mlstm_scan(proj, out, batch, state, heads=H, dim=kd, vdim=vd, gate_cap=10.0, q_scale=kd ** -0.5,
                                              columns=cols, i_bias=zero, f_bias=zero, chunked=chunked)
             nbytes = n_seg * H * size * 4 * 2 + M * (2 * H * kd + 2 * H * vd + 2 * H) * 4
             flops = 4 * M * H * kd * vd
@@ -345,7 +345,7 @@ def main(argv=None):
             def make_join(M=M):
                 y, h, g1, g2 = torch.randn((M, dm), device=dev), torch.randn((M, dm), device=dev), torch.ones(dm, device=dev), torch.ones(dm, device=dev)
                 x = torch.empty((M, dm), dtype=bf, device=dev)
-                return lambda: ks.rms_norm_residual(y, g1, 1e-6, 0.3, h, next_gain=g2, next_out=x)
+                return lambda: ks.rms_norm_residual(y, g1, 1e-5, 0.5, h, next_gain=g2, next_out=x)
             nbytes = M * dm * (4 + 4 + 4 + 2)
             report("recurrent", f"rms_norm_residual with the next norm M={M} d={dm}", timed_rotating(make_join, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
 
