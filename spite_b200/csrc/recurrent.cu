@@ -177,12 +177,14 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmParams p) {
 // With F_t the sum of the log forget gates from the chunk's first token to t, a_s = i_s - F_s, m0 the maximum the chunk
 // starts from and M_t = max(m0, max_{s<=t} a_s), the recurrence unrolls to m_t = F_t + M_t and
 //     S_t = exp(m0 - M_t) S_0 + sum_{s<=t} exp(a_s - M_t) k_s v_s^T                 (n_t alike)
-// so a chunk is three small matrix products in float32 on the CUDA cores, none of which waits for a token before it:
-//     [q S_0 | q n_0 | q k^T]   (tokens x (32 value columns, 1, 32 keys), over the key rows),
+// so a chunk is small matrix products in float32 on the CUDA cores, none of which waits for a token before it:
+//     q k^T and the gates' a_s, F_t   (they do not depend on the state: a kernel of its own computes them for every
+//                                      chunk and head of the step at once, into working memory),
+//     [q S_0 | q n_0]                 (tokens x (32 value columns, 1), over the key rows),
 //     numerators = exp(m0 - M_t) q S_0 + sum_{s<=t} exp(a_s - M_t) (q_t . k_s) v_s   (the denominator's n . q alike),
 //     S <- exp(m0 - M_last) S + sum_s exp(a_s - M_last) k_s v_s^T.
-// Every exponent is <= 0.  A block owns 32 value columns of one (segment, head), as in the kernel above, with the
-// state tile, the chunk's q, k and v in shared memory; 256 threads.
+// Every exponent is <= 0.  In the second kernel a block owns 32 value columns of one (segment, head), as in the kernel
+// above, with the state tile, the chunk's q, k and v in shared memory; 256 threads.
 constexpr int CL = 32;            // tokens of a chunk
 constexpr int SROW = 36;          // floats of a row of the state tile: 32 value columns, n, three zeros
 
@@ -209,6 +211,92 @@ __device__ __forceinline__ double warp_prefix_max(double v, int lane) {
     return v;
 }
 
+constexpr int CHUNK_RECORD = CL * CL + 4 * CL;   // floats a chunk and head: q k^T [CL][CL], then a_s and F_t as doubles, each [CL]
+
+// the number of chunks of the segments before `seg` (chunks are numbered segment by segment)
+__device__ __forceinline__ int chunks_before(const int* cu_seqlens, int seg) {
+    int n = 0;
+    for (int s = 0; s < seg; ++s) n += (cu_seqlens[s + 1] - cu_seqlens[s] + CL - 1) / CL;
+    return n;
+}
+
+// What a chunk needs that does not depend on the state: the scores q_t . k_s (s <= t, q not yet scaled) and, from the
+// gates, F_t and a_s = i_s - F_s as doubles (-1e300 behind the segment's end).  One block a (chunk, head).
+template <int RPL2>
+__global__ void __launch_bounds__(256) mlstm_scores_kernel(const MlstmParams p, float* __restrict__ scratch) {
+    constexpr int DP = 64 * RPL2, ROW = DP + 4;
+    extern __shared__ __align__(16) float sm[];
+    float* q_s = sm;                              // [CL][ROW]
+    float* k_s = q_s + CL * ROW;                  // [CL][ROW]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int head = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int seg = 0, rest = blockIdx.x;
+    for (; seg < p.n_segments; ++seg) {
+        const int n = (p.cu_seqlens[seg + 1] - p.cu_seqlens[seg] + CL - 1) / CL;
+        if (rest < n) break;
+        rest -= n;
+    }
+    if (seg >= p.n_segments) return;
+    const int c0 = p.cu_seqlens[seg] + rest * CL, len = min(CL, p.cu_seqlens[seg + 1] - c0), dim = p.dim;
+    float* rec = scratch + ((size_t)blockIdx.x * p.heads + head) * CHUNK_RECORD;
+    const float* rows = p.proj + (size_t)c0 * p.stride;
+    const bool vec4 = (dim % 4) == 0 && (p.stride % 4) == 0 && (p.q_col % 4) == 0 && (p.k_col % 4) == 0 && (((uintptr_t)p.proj) & 15) == 0;
+    if (vec4) {
+#pragma unroll 4
+        for (int e = tid; e < CL * (DP / 4); e += 256) {
+            const int t = e / (DP / 4), d = (e - t * (DP / 4)) * 4;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            if (t < len && d < dim) {
+                a = *(const float4*)&rows[(size_t)t * p.stride + p.q_col + head * dim + d];
+                b = *(const float4*)&rows[(size_t)t * p.stride + p.k_col + head * dim + d];
+            }
+            *(float4*)&q_s[t * ROW + d] = a;
+            *(float4*)&k_s[t * ROW + d] = b;
+        }
+    } else {
+        for (int e = tid; e < CL * DP; e += 256) {
+            const int t = e / DP, d = e - t * DP;
+            const bool on = t < len && d < dim;
+            q_s[t * ROW + d] = on ? rows[(size_t)t * p.stride + p.q_col + head * dim + d] : 0.f;
+            k_s[t * ROW + d] = on ? rows[(size_t)t * p.stride + p.k_col + head * dim + d] : 0.f;
+        }
+    }
+    if (warp == 0) {
+        const bool on = lane < len;
+        const float bi = p.i_bias ? p.i_bias[head] : 0.f, bf = p.f_bias ? p.f_bias[head] : 0.f;
+        const float cap = p.gate_cap, inv_cap = 1.0f / p.gate_cap;
+        float ig = 0.f, fg = 0.f;
+        if (on) {
+            ig = cap * tanhf((rows[(size_t)lane * p.stride + p.i_col + head] + bi) * inv_cap);
+            fg = log_sigmoid(cap * tanhf((rows[(size_t)lane * p.stride + p.f_col + head] + bf) * inv_cap));
+        }
+        const double F = warp_prefix_sum((double)fg, lane);
+        double* gd = reinterpret_cast<double*>(rec + CL * CL);
+        gd[lane] = on ? (double)ig - F : -1.0e300;
+        gd[CL + lane] = F;
+    }
+    __syncthreads();
+    {   // a thread has one token and the keys sg, sg + 8, ... (rows 8 apart: eight lanes read eight banks' worth)
+        const int t = tid >> 3, sg = tid & 7;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (t < len) {
+            for (int d = 0; d < DP; d += 4) {
+                const float4 qv = *(const float4*)&q_s[t * ROW + d];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (sg + 8 * j > t) continue;
+                    const float4 kv = *(const float4*)&k_s[(sg + 8 * j) * ROW + d];
+                    acc[j] = fmaf(qv.x, kv.x, acc[j]); acc[j] = fmaf(qv.y, kv.y, acc[j]);
+                    acc[j] = fmaf(qv.z, kv.z, acc[j]); acc[j] = fmaf(qv.w, kv.w, acc[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rec[t * CL + sg + 8 * j] = acc[j];
+    }
+}
+
 __device__ __forceinline__ void copy16_async(void* smem, const void* gmem, int src_bytes) {     // the rest of the 16 bytes: zeros
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(src_bytes) : "memory");
@@ -217,7 +305,7 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 template <int RPL2>
-__global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(const MlstmParams p) {
+__global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(const MlstmParams p, const float* __restrict__ scratch) {
     constexpr int DP = ChunkSmem<RPL2>::DP;
     extern __shared__ __align__(16) float sm[];
     float* S_s = sm;                              // [DP][SROW]: the state's 32 columns, then n
@@ -226,8 +314,8 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
     float* q_s = S_s + DP * SROW;                 // (not yet scaled: q_scale multiplies the sums)
     float* k_s = q_s + CL * DP;                   // [CL][DP]
     float* v_s = k_s + CL * DP;                 // [CL][32]: the block's value columns
-    float* X0 = v_s + CL * CL;                    // [CL][32]: q S_0, first half the sums, then scaled by exp(m0 - M_t)
-    float* X1 = X0 + CL * CL;                     // [CL][CL]: q k^T, first half the sums, then weighted and masked
+    float* X0 = v_s + CL * CL;                    // [CL][32]: q S_0 scaled by exp(m0 - M_t)
+    float* X1 = X0 + CL * CL;                     // [CL][CL]: q k^T, then weighted and masked
     // a_s and M_t as doubles: they are differences of sums over the chunk's gates, and exp(a_s - M_t) is to be as exact
     // as exp of a single gate in the walk token by token, also where the gates are large
     double* g_a = reinterpret_cast<double*>(X1 + CL * CL);
@@ -263,8 +351,6 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
         S_s[e] = x;
     }
     float m_run = st_n[dim];
-    const float bi = p.i_bias ? p.i_bias[head] : 0.f, bf = p.f_bias ? p.f_bias[head] : 0.f;
-    const float cap = p.gate_cap, inv_cap = 1.0f / p.gate_cap;
     // q and k rows move as groups of four floats where every such group is aligned
     const bool vec4 = (dim % 4) == 0 && (p.stride % 4) == 0 && (p.q_col % 4) == 0 && (p.k_col % 4) == 0 && (((uintptr_t)p.proj) & 15) == 0;
 
@@ -283,8 +369,11 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
         }
         copy_async_commit();
     };
-    float v_next[4], gi_next = 0.f, gf_next = 0.f;
-    auto fetch_small = [&](int c) {
+    float v_next[4];
+    float4 qk_next = make_float4(0.f, 0.f, 0.f, 0.f);        // four of the chunk's scores: token tid / 8, keys 4 (tid % 8) ...
+    double a_next = 0.0, F_next = 0.0;                        // warp 0: a lane a token
+    int chunk_id = chunks_before(p.cu_seqlens, seg);
+    auto fetch_small = [&](int c, int chunk) {
         if (c >= t1) return;
         const float* rows = p.proj + (size_t)c * p.stride;
         const int len = min(CL, t1 - c);
@@ -293,16 +382,19 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
             const int e = tid + 256 * i, t = e >> 5, cc = e & 31;
             v_next[i] = (t < len && cb0 + cc < vdim) ? rows[(size_t)t * p.stride + p.v_col + head * vdim + cb0 + cc] : 0.f;
         }
-        if (warp == 0 && lane < len) {
-            gi_next = rows[(size_t)lane * p.stride + p.i_col + head];
-            gf_next = rows[(size_t)lane * p.stride + p.f_col + head];
+        const float* rec = scratch + ((size_t)chunk * p.heads + head) * CHUNK_RECORD;
+        qk_next = *(const float4*)&rec[tid * 4];
+        if (warp == 0) {
+            const double* gd = reinterpret_cast<const double*>(rec + CL * CL);
+            a_next = gd[lane];
+            F_next = gd[CL + lane];
         }
     };
     fetch_rows(t0, p.q_col, q_s, true);
     fetch_rows(t0, p.k_col, k_s, false);
-    fetch_small(t0);
+    fetch_small(t0, chunk_id);
 
-    for (int c0 = t0; c0 < t1; c0 += CL) {
+    for (int c0 = t0; c0 < t1; c0 += CL, ++chunk_id) {
         const int len = min(CL, t1 - c0);
         // ---- the chunk's q, k and v are in place; the gates and what follows from them (warp 0, a lane a token)
         if (vec4) copy_async_wait_all();
@@ -317,15 +409,10 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) v_s[tid + 256 * i] = v_next[i];
+        *(float4*)&X1[tid * 4] = qk_next;
         if (warp == 0) {
             const bool on = lane < len;
-            float ig = 0.f, fg = 0.f;
-            if (on) {
-                ig = cap * tanhf((gi_next + bi) * inv_cap);
-                fg = log_sigmoid(cap * tanhf((gf_next + bf) * inv_cap));
-            }
-            const double F = warp_prefix_sum((double)fg, lane);
-            const double a = on ? (double)ig - F : -1.0e300;
+            const double a = a_next, F = F_next;
             const double M = fmax((double)m_run, warp_prefix_max(a, lane));
             const double M_last = __shfl_sync(0xffffffffu, M, len - 1), F_last = __shfl_sync(0xffffffffu, F, len - 1);
             g_a[lane] = a;
@@ -342,59 +429,46 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
         }
         __syncthreads();
 
-        // ---- [q S_0 | q k^T]: a thread has 4 tokens (tg, tg + 8, ...) by 4 columns, over half of the key rows
-        const int kh = tid >> 7, w4 = warp & 3, tg = lane & 7, cg = (lane >> 3) + 4 * (w4 & 1);
-        const bool keys = w4 >= 2;
-        float acc[4][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        // ---- q S_0: a thread has 4 tokens (tg, tg + 8, ...) by 4 columns over a quarter of the key rows (every fourth
+        // group of four); the quarters meet by shuffles, and the lane of quarter kq writes token tg + 8 kq
         {
-            const int d_lo = kh * (DP / 2), d_hi = d_lo + DP / 2;
-            if (!keys) {
-                for (int d = d_lo; d < d_hi; d += 4) {
-                    float4 qv[4], sv[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) qv[i] = *(const float4*)&q_s[(tg + 8 * i) * DP + (d ^ (tg << 2))];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sv[e] = *(const float4*)&S_s[(d + e) * SROW + 4 * cg];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float qe[4] = {qv[i].x, qv[i].y, qv[i].z, qv[i].w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            acc[i][0] = fmaf(qe[e], sv[e].x, acc[i][0]);
-                            acc[i][1] = fmaf(qe[e], sv[e].y, acc[i][1]);
-                            acc[i][2] = fmaf(qe[e], sv[e].z, acc[i][2]);
-                            acc[i][3] = fmaf(qe[e], sv[e].w, acc[i][3]);
-                        }
-                    }
-                }
-            } else {
-                for (int d = d_lo; d < d_hi; d += 4) {
-                    float4 qv[4], kv[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) qv[i] = *(const float4*)&q_s[(tg + 8 * i) * DP + (d ^ (tg << 2))];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) kv[j] = *(const float4*)&k_s[(4 * cg + j) * DP + d];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            acc[i][j] = fmaf(qv[i].x, kv[j].x, acc[i][j]);
-                            acc[i][j] = fmaf(qv[i].y, kv[j].y, acc[i][j]);
-                            acc[i][j] = fmaf(qv[i].z, kv[j].z, acc[i][j]);
-                            acc[i][j] = fmaf(qv[i].w, kv[j].w, acc[i][j]);
-                        }
-                }
-            }
-        }
-        float* X = keys ? X1 : X0;
-        if (kh == 1) {
+            const int kq = lane >> 3, tg = lane & 7, cg = warp;
+            float acc[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                *(float4*)&X[(tg + 8 * i) * CL + 4 * cg] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+            for (int d = 4 * kq; d < DP; d += 16) {
+                float4 qv[4], sv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qv[i] = *(const float4*)&q_s[(tg + 8 * i) * DP + (d ^ (tg << 2))];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sv[e] = *(const float4*)&S_s[(d + e) * SROW + 4 * cg];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float qe[4] = {qv[i].x, qv[i].y, qv[i].z, qv[i].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc[i][0] = fmaf(qe[e], sv[e].x, acc[i][0]);
+                        acc[i][1] = fmaf(qe[e], sv[e].y, acc[i][1]);
+                        acc[i][2] = fmaf(qe[e], sv[e].z, acc[i][2]);
+                        acc[i][3] = fmaf(qe[e], sv[e].w, acc[i][3]);
+                    }
+                }
+            }
+            float mine[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float x = acc[i][j];
+                    x += __shfl_xor_sync(0xffffffffu, x, 8);
+                    x += __shfl_xor_sync(0xffffffffu, x, 16);
+                    if (i == kq) mine[j] = x;
+                }
+            const int t = tg + 8 * kq;
+            const float g = g_g[t] * p.q_scale;
+            *(float4*)&X0[t * CL + 4 * cg] = make_float4(mine[0] * g, mine[1] * g, mine[2] * g, mine[3] * g);
         }
         // q . n_0 for token tid / 8: each of its 8 threads sums an eighth of the key rows (the same threads write the token's outputs)
         float nq0 = 0.f;
@@ -402,30 +476,18 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
         nq0 += __shfl_xor_sync(0xffffffffu, nq0, 1);
         nq0 += __shfl_xor_sync(0xffffffffu, nq0, 2);
         nq0 += __shfl_xor_sync(0xffffffffu, nq0, 4);
+        {   // the scores of the thread's token and four keys: weighted, masked
+            const int t = tid >> 3, s0 = (tid & 7) * 4;
+            const double M = g_M[t];
+            const float4 x = *(const float4*)&X1[tid * 4];
+            float r[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[j] = (s0 + j <= t && s0 + j < len) ? expf((float)(g_a[s0 + j] - M)) * (r[j] * p.q_scale) : 0.f;
+            *(float4*)&X1[tid * 4] = make_float4(r[0], r[1], r[2], r[3]);
+        }
         __syncthreads();
         fetch_rows(c0 + CL, p.q_col, q_s, true);      // (nothing reads this chunk's q any more)
-        fetch_small(c0 + CL);
-        if (kh == 0) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int t = tg + 8 * i;
-                const float4 o = *(const float4*)&X[t * CL + 4 * cg];
-                float r[4] = {acc[i][0] + o.x, acc[i][1] + o.y, acc[i][2] + o.z, acc[i][3] + o.w};
-                if (!keys) {
-                    const float g = g_g[t] * p.q_scale;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) r[j] *= g;
-                } else {
-                    const double M = g_M[t];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int s = 4 * cg + j;
-                        r[j] = (s <= t && s < len) ? expf((float)(g_a[s] - M)) * (r[j] * p.q_scale) : 0.f;
-                    }
-                }
-                *(float4*)&X[t * CL + 4 * cg] = make_float4(r[0], r[1], r[2], r[3]);
-            }
-        }
+        fetch_small(c0 + CL, chunk_id + 1);
 
         // ---- the state after the chunk: a warp has 8 columns (warps 0..3 and 4..7: the two halves of the key rows),
         // a lane the rows lane, lane + 32, ...; the warps of the first columns also renew n
@@ -499,19 +561,25 @@ __global__ void __launch_bounds__(256, RPL2 <= 4 ? 2 : 1) mlstm_chunk_kernel(con
 }
 
 template <int RPL2>
-int launch_mlstm_chunk(const MlstmParams& p, dim3 grid, cudaStream_t st) {
+int launch_mlstm_chunk(const MlstmParams& p, float* scratch, int scratch_chunks, dim3 grid, cudaStream_t st) {
+    const size_t smem_scores = (size_t)2 * CL * (64 * RPL2 + 4) * sizeof(float);
     const size_t smem = (size_t)ChunkSmem<RPL2>::FLOATS * sizeof(float);
+    auto scores = mlstm_scores_kernel<RPL2>;
     auto k = mlstm_chunk_kernel<RPL2>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(scores, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scores) != cudaSuccess ||
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
-    SPITE_LAUNCH(k, grid, 256, smem, st, p);
+    SPITE_LAUNCH(scores, dim3(scratch_chunks, p.heads), 256, smem_scores, st, p, scratch);
+    // (an ordinary launch: as a programmatic dependent of the scores' kernel, whose blocks let dependents start at
+    // once, the pair took 925 us for a prompt of 2,048 tokens where it takes 599 us)
+    k<<<grid, 256, smem, st>>>(p, (const float*)scratch);
     return spite_launch_status();
 }
 
 }  // namespace
 
-SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
+static int mlstm_scan_launch(const MlstmParams* p, float* scratch, int scratch_chunks, void* stream) {
     if (!p || !p->proj || !p->out || !p->state || !p->cu_seqlens || !p->slots) return SPITE_BAD_ARG;
     if (p->n_segments < 0 || p->heads < 1 || p->dim < 1 || p->vdim < 1 || !(p->gate_cap > 0.f) || !(p->q_scale == p->q_scale))
         return SPITE_BAD_ARG;
@@ -526,10 +594,11 @@ SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
     dim3 grid((p->vdim + COLS_PER_BLOCK - 1) / COLS_PER_BLOCK, p->heads, p->n_segments);
     cudaStream_t st = (cudaStream_t)stream;
     if (p->chunked) {
-        if (p->dim <= 64) return launch_mlstm_chunk<1>(*p, grid, st);
-        if (p->dim <= 128) return launch_mlstm_chunk<2>(*p, grid, st);
-        if (p->dim <= 256) return launch_mlstm_chunk<4>(*p, grid, st);
-        return launch_mlstm_chunk<8>(*p, grid, st);
+        if (!scratch || scratch_chunks < 1 || (((uintptr_t)scratch) & 15)) return SPITE_BAD_ARG;
+        if (p->dim <= 64) return launch_mlstm_chunk<1>(*p, scratch, scratch_chunks, grid, st);
+        if (p->dim <= 128) return launch_mlstm_chunk<2>(*p, scratch, scratch_chunks, grid, st);
+        if (p->dim <= 256) return launch_mlstm_chunk<4>(*p, scratch, scratch_chunks, grid, st);
+        return launch_mlstm_chunk<8>(*p, scratch, scratch_chunks, grid, st);
     }
     if (p->dim <= 32) SPITE_LAUNCH(mlstm_scan_kernel<1>, grid, 128, 0, st, *p);
     else if (p->dim <= 64) SPITE_LAUNCH(mlstm_scan_kernel<2>, grid, 128, 0, st, *p);
@@ -537,4 +606,15 @@ SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
     else if (p->dim <= 256) SPITE_LAUNCH(mlstm_scan_kernel<8>, grid, 128, 0, st, *p);
     else SPITE_LAUNCH(mlstm_scan_kernel<16>, grid, 128, 0, st, *p);
     return spite_launch_status();
+}
+
+SPITE_API int spite_mlstm_scan(const MlstmParams* p, void* stream) {
+    if (p && p->chunked) return SPITE_BAD_ARG;            // (32 tokens at a time needs working memory: the entry below)
+    return mlstm_scan_launch(p, nullptr, 0, stream);
+}
+
+// `scratch`: [scratch_chunks, heads, 1152] floats of working memory, 16-byte aligned; scratch_chunks >= the step's
+// chunks, the sum over the segments of ceil(tokens / 32).  Takes p->chunked as it is given.
+SPITE_API int spite_mlstm_scan_chunked(const MlstmParams* p, float* scratch, int scratch_chunks, void* stream) {
+    return mlstm_scan_launch(p, scratch, scratch_chunks, stream);
 }

@@ -930,8 +930,15 @@ class CudaKernels(KernelSet):
                         state=state.data_ptr(), head_stride=state.shape[2], cu_seqlens=batch.cu_seqlens.data_ptr(),
                         slots=batch.slots.data_ptr(), n_segments=n_seg, heads=int(heads), dim=int(dim), vdim=int(vdim),
                         gate_cap=float(gate_cap), q_scale=float(q_scale), chunked=int(bool(chunked)))
-        st = self._lib("recurrent").spite_mlstm_scan(C.byref(p), self._stream())
-        self._count("recurrent", 1)
+        if chunked:
+            # working memory for what the chunks need ahead of the state (scores, sums of the gates): a record for every
+            # chunk and head; the segments' chunks are at most tokens / 32 + segments
+            n_chunks = (M + 31) // 32 + n_seg
+            scratch = torch.empty((n_chunks, heads, 1152), dtype=torch.float32, device=proj.device)
+            st = self._lib("recurrent").spite_mlstm_scan_chunked(C.byref(p), C.c_void_p(scratch.data_ptr()), C.c_int(n_chunks), self._stream())
+        else:
+            st = self._lib("recurrent").spite_mlstm_scan(C.byref(p), self._stream())
+        self._count("recurrent", 2 if chunked else 1)
         _check(st, "mlstm_scan")
 
     # ------------------------------------------------------------------ mixture of experts
