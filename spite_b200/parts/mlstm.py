@@ -9,9 +9,10 @@ and carried from token to token in float32 in the request's state slot:
     o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
     out = W_o [ (o_h / rms(o_h)) for every head, concatenated, * gain * sigmoid(W_g x) ]
 
-One product makes q, k, v, the gate's columns and the two gates' pre-activations as float32 sums; the scan kernel
-walks every segment of the step from its slot's state; one kernel norms the heads and applies gain and gate; the
-output projection adds into (or fills) the float32 stream.
+One product makes q, k, v, the gate's columns and the two gates' pre-activations as float32 sums; the scan walks
+every segment of the step from its slot's state (token by token in decode steps, 32 tokens at a time where the step
+has prompt portions: the same recurrence unrolled over a chunk, see `csrc/recurrent.cu`); one kernel norms the heads
+and applies gain and gate; the output projection adds into (or fills) the float32 stream.
 """
 from __future__ import annotations
 
