@@ -183,6 +183,50 @@ def test_memory_keeps_a_token_from_hundreds_of_steps_back():
         close(out.view(T, heads, vdim), ref, 1e-3, "against loops in float64")
 
 
+def test_malformed_scan_calls_launch_nothing():
+    """Null pointers and sizes that make no sense return -1, key heads beyond the kernels' 512 rows -2, the chunked walk
+    without working memory (or through the entry that has none) -1; the outputs keep their canary."""
+    import ctypes as C
+    from spite_b200.kernels import build
+    from spite_b200.kernels.cuda import MlstmParams
+    lib = build.load("recurrent")
+    heads, dim, vdim, M = 2, 16, 24, 5
+    proj = torch.zeros((M, 2 * heads * dim + heads * vdim + 2 * heads), device=DEV)
+    out = torch.full((M, heads * vdim), 96.5, device=DEV)
+    state = torch.full((1, heads, CudaSize.state(dim, vdim)), 96.5, device=DEV)
+    cu = torch.tensor([0, M], dtype=torch.int32, device=DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    zero = torch.zeros(heads, device=DEV)
+    scratch = torch.zeros((2, heads, 1152), device=DEV)
+
+    def params(**change):
+        kw = dict(proj=proj.data_ptr(), stride=proj.shape[1], q_col=0, k_col=heads * dim, v_col=2 * heads * dim,
+                  i_col=2 * heads * dim + heads * vdim, f_col=2 * heads * dim + heads * vdim + heads, i_bias=zero.data_ptr(),
+                  f_bias=zero.data_ptr(), out=out.data_ptr(), state=state.data_ptr(), head_stride=state.shape[2],
+                  cu_seqlens=cu.data_ptr(), slots=slots.data_ptr(), n_segments=1, heads=heads, dim=dim, vdim=vdim,
+                  gate_cap=10.0, q_scale=0.25, chunked=0)
+        kw.update(change)
+        return MlstmParams(**kw)
+
+    plain = lambda p: lib.spite_mlstm_scan(C.byref(p), None)
+    chunk = lambda p, s=scratch, n=2: lib.spite_mlstm_scan_chunked(C.byref(p), C.c_void_p(None if s is None else s.data_ptr()), C.c_int(n), None)
+    cases = [(plain(params(proj=None)), -1), (plain(params(out=None)), -1), (plain(params(state=None)), -1),
+             (plain(params(heads=0)), -1), (plain(params(gate_cap=0.0)), -1), (plain(params(stride=3)), -1),
+             (plain(params(head_stride=dim * vdim)), -1), (plain(params(dim=513, stride=10 ** 6, head_stride=10 ** 9)), -2),
+             (plain(params(chunked=1)), -1), (chunk(params(chunked=1), None), -1), (chunk(params(chunked=1), scratch, 0), -1),
+             (chunk(params(chunked=1, slots=None)), -1)]
+    torch.cuda.synchronize()
+    assert [got for got, _ in cases] == [want for _, want in cases]
+    assert bool((out == 96.5).all()) and bool((state == 96.5).all())
+
+
+class CudaSize:
+    @staticmethod
+    def state(dim, vdim):
+        from spite_b200.kernels.api import KernelSet
+        return KernelSet.mlstm_state_size(dim, vdim)
+
+
 # ---------------------------------------------------------------------------- between the heads and the output projection
 @pytest.mark.parametrize("dtype,in32", [(torch.float32, True), (torch.bfloat16, True), (torch.bfloat16, False), (torch.float32, False)])
 @pytest.mark.parametrize("heads,size,norm,gain,gate", [(3, 12, True, True, True), (1, 70, True, True, True), (4, 64, False, False, True),
