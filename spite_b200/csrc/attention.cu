@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     // tokens of 56 heads; one head a warp with more blocks, 51 us.)
     const bool norm = p.qk_norm_eps > 0.f;
     const bool norm_first = norm && p.norm_before_rotation;
+    const float norm_n = (float)(p.norm_dim > 0 ? p.norm_dim : hd);
     for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
         const T* in = (const T*)p.qkv + (size_t)t * p.qkv_stride + (size_t)head * hd;
         const bool is_q = head < nq, is_v = head >= nq + nkv;
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
 #pragma unroll
             for (int r = 0; r < MAXP; ++r) ss += x0[r] * x0[r] + x1[r] * x1[r];
             ss = warp_sum(ss);
-            const float mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
+            const float mul = 1.0f / sqrtf(ss / norm_n + p.qk_norm_eps);
 #pragma unroll
             for (int r = 0; r < MAXP; ++r) {
                 if (2 * (lane + 32 * r) >= hd) continue;
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
         float mul = 1.f;
         if (norm && !norm_first) {
             ss = warp_sum(ss);
-            mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
+            mul = 1.0f / sqrtf(ss / norm_n + p.qk_norm_eps);
         }
         if (is_q) mul *= temp;
 #pragma unroll
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionPar
             const T* k = kbase + row;
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32(k[d]), dot);
-            s = dot * p.softmax_scale - slope * (float)(pos - j);
+            s = capped(p, dot * p.softmax_scale) - slope * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);                  // 0 on the first tile (m = -inf)

@@ -61,6 +61,8 @@ struct QkPrepareParams {
     // output before anything else happens to it (null: none)
     const float* bias;
     int q_only;                 // the rows of qkv hold the q heads alone: this layer reads keys and values that another layer cached
+    int norm_dim;               // > 0: a q or k head has this many elements (the rest of its head_dim are padding zeros): the
+                                // per-head norm's mean is taken over them (0: over head_dim)
 };
 
 struct AttentionParams {
@@ -77,6 +79,7 @@ struct AttentionParams {
     const float* head_gates;    // [tokens, num_heads] or null: head h's output of token t is multiplied by head_gates[t * nq + h]
     int out_by_head_tokens;     // 0: out is [tokens, num_heads, head_dim]; n > 0: out is [num_heads, n, head_dim], head by head
                                 // (n the tokens of the step), the order in which a product per head reads its rows
+    float score_softcap;        // > 0: a scaled score s becomes cap * tanh(s / cap) before bias, mask and softmax
 };
 
 // Where the output row of (token, head) starts, in rows of head_dim elements.
@@ -91,6 +94,10 @@ __device__ __forceinline__ float sink_of(const AttentionParams& p, int head) {
 // What is taken off the score of a key `distance` positions before the query.
 __device__ __forceinline__ float slope_of(const AttentionParams& p, int head) {
     return p.head_slopes ? p.head_slopes[head] : 0.f;
+}
+// A scaled score squashed into (-cap, cap), or itself without a cap.
+__device__ __forceinline__ float capped(const AttentionParams& p, float s) {
+    return p.score_softcap > 0.f ? p.score_softcap * tanhf(s / p.score_softcap) : s;
 }
 // The factor on a finished output row.
 __device__ __forceinline__ float gate_of(const AttentionParams& p, int token, int head) {

@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
                         for (int e = 0; e < 2; ++e) {
                             const int j = j0 + 8 * n + 2 * cc + e;
                             const bool vis = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                            const float v = vis ? sc[n][2 * h + e] * p.softmax_scale - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
+                            const float v = vis ? capped(p, sc[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                             sc[n][2 * h + e] = v;
                             mx = fmaxf(mx, v);
                         }

@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + 8 * n + 2 * cc + e;
                     const bool ok = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                    const float v = ok ? s[n][2 * h + e] * p.softmax_scale - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
+                    const float v = ok ? capped(p, s[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                     s[n][2 * h + e] = v;
                     mx = fmaxf(mx, v);
                 }

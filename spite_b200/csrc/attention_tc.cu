@@ -306,6 +306,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 // the scale afterwards): its rounding error is relative to the bias itself
                 const bool biased = p.head_slopes != nullptr;
                 const float bias_raw = slope_of(p, head) / p.softmax_scale;
+                // a cap on the scaled scores, in units of the raw ones; the argument of 2^x that gives e^(2 s scale / cap)
+                const float cap_raw = p.score_softcap > 0.f ? p.score_softcap / p.softmax_scale : 0.f;
+                const float cap_arg = p.score_softcap > 0.f ? 2.f * LOG2E * p.softmax_scale / p.score_softcap : 0.f;
                 const unsigned lane_base = tmem_g + ((unsigned)(quarter * 32) << 16);
                 float m_ref = -INFINITY, l = 0.f;
                 bool ok = true;
@@ -324,6 +327,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     // element with a constant that the compiler knows; the first is the same for the whole tile and joins
                     // the maximum and the exponent's offset below.
                     const float tile_bias = biased ? bias_raw * (float)(j0 - pos) : 0.f;
+                    if (cap_raw > 0.f) {
+                        // cap tanh(s scale / cap) in units of the raw scores: tanh(x) = 1 - 2 / (e^(2x) + 1), whose absolute
+                        // error (a few float32 roundings of a number below one) times the cap is far below a bfloat16 weight's
+#pragma unroll
+                        for (int e = 0; e < BN; ++e)
+                            s[e] = fmaf(-2.f * cap_raw, __frcp_rn(ex2(s[e] * cap_arg) + 1.f), cap_raw);
+                    }
                     if (biased) {
 #pragma unroll
                         for (int e = 0; e < BN; ++e) s[e] = fmaf(bias_raw, (float)e, s[e]);

@@ -342,6 +342,7 @@ SPITE_API int spite_rms_norm(int out_dtype, const float* x, const float* gain, c
 //     h[m, :] += mult * y[m, :] * rsqrt(mean(y[m]^2) + eps) * gain
 // and, if `next_out` is given, the norm that the next sublayer reads, of the row just made:
 //     next_out[m, :] = h[m, :] * rsqrt(mean(h[m]^2) + eps) * next_gain
+// (without `next_gain`: the row itself in the output type, for a sublayer that reads the stream unnormed)
 // One block per row; the row (y, then h) stays in registers between the sums and the scalings, VPT groups of four
 // elements a thread.  All sums float32.
 template <typename T, int VPT>
@@ -380,9 +381,17 @@ __global__ void rms_norm_residual_vec_kernel(const float* __restrict__ y, const 
         }
     }
     if (!next_out) return;
+    T* out = next_out + m * d;
+    if (!next_gain) {                                          // the next sublayer reads the row itself, not its norm
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < d4) store4(out + 4 * c, r[k].x, r[k].y, r[k].z, r[k].w);
+        }
+        return;
+    }
     s2 = block_sum(s2, scratch);
     const float scale2 = 1.0f / sqrtf(s2 / (float)d + eps);
-    T* out = next_out + m * d;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
@@ -415,16 +424,20 @@ __global__ void rms_norm_residual_kernel(const float* __restrict__ y, const floa
         s2 += v * v;
     }
     if (!next_out) return;
+    T* out = next_out + m * d;
+    if (!next_gain) {                                          // the next sublayer reads the row itself, not its norm
+        for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(hr[c]);
+        return;
+    }
     s2 = block_sum(s2, scratch);
     const float scale2 = 1.0f / sqrtf(s2 / (float)d + eps);
-    T* out = next_out + m * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(hr[c] * scale2 * next_gain[c]);
 }
 
 SPITE_API int spite_rms_norm_residual(int out_dtype, const float* y, const float* gain, float* h, const float* next_gain,
                                       void* next_out, int n_rows, int d, float eps, float mult, void* stream) {
     if (!y || !gain || !h || n_rows < 0 || d <= 0 || !(eps > 0.f) || !(mult == mult)) return SPITE_BAD_ARG;
-    if ((next_out != nullptr) != (next_gain != nullptr)) return SPITE_BAD_ARG;
+    if (next_gain && !next_out) return SPITE_BAD_ARG;          // (an output without a gain: the row itself, not its norm)
     if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
     if (n_rows == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
@@ -474,13 +487,16 @@ SPITE_API int spite_fill_rows(float* out, const float* vec, int n_rows, int d, i
 
 // What stands between a mixer's heads and its output projection:
 //     out[m, h * size + j] = x[m, h * size + j] * r_mh * gain[h * size + j] * sigmoid(gates[m, h * size + j])
+// (`gate_silu`: times z sigmoid(z) of the gate column z instead; without `gain_per_head` the gain has `size` elements
+// that all heads share)
 // r_mh = rsqrt(mean_j(x[m, h, :]^2) + eps) if eps > 0, else 1; gain and gates may be null (a factor of one).
 // `gates` has rows of `gate_stride` elements (the gate columns of a wider product).  One warp per (token, head); the
 // head's elements stay in registers between the sum and the scaling while they are few enough.
 template <typename TX, typename TO>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const TX* __restrict__ x, const TX* __restrict__ gates,
                                                              long long gate_stride, const float* __restrict__ gain,
-                                                             TO* __restrict__ out, int n_tokens, int heads, int size, float eps) {
+                                                             TO* __restrict__ out, int n_tokens, int heads, int size, float eps,
+                                                             int gate_silu, int gain_per_head) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -498,12 +514,15 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const TX* __restric
         mul = 1.0f / sqrtf(s / (float)size + eps);
     }
     const TX* g = gates ? gates + (size_t)m * gate_stride + (size_t)h * size : nullptr;
-    const float* w = gain ? gain + (size_t)h * size : nullptr;
+    const float* w = gain ? gain + (gain_per_head ? (size_t)h * size : 0) : nullptr;
     TO* o = out + base;
     for (int j = lane; j < size; j += 32) {
         float v = to_f32(in[j]) * mul;
         if (w) v *= w[j];
-        if (g) v *= 1.0f / (1.0f + expf(-to_f32(g[j])));
+        if (g) {
+            const float z = to_f32(g[j]), sg = 1.0f / (1.0f + expf(-z));
+            v *= gate_silu ? z * sg : sg;
+        }
         o[j] = from_f32<TO>(v);
     }
 }
@@ -511,7 +530,8 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const TX* __restric
 // x_dtype: type of x and gates; out_dtype: type of out (x may be the float32 result of a recurrence while out feeds a
 // bfloat16 product); out may be x.
 SPITE_API int spite_head_norm_gate(int x_dtype, int out_dtype, const void* x, const void* gates, long long gate_stride,
-                                   const float* gain, void* out, int n_tokens, int heads, int size, float eps, void* stream) {
+                                   const float* gain, void* out, int n_tokens, int heads, int size, float eps, int gate_silu,
+                                   int gain_per_head, void* stream) {
     if (!x || !out || n_tokens < 0 || heads < 1 || size < 1 || !(eps == eps) || eps < 0.f) return SPITE_BAD_ARG;
     if (gates && gate_stride < (long long)heads * size) return SPITE_BAD_ARG;
     if (x_dtype != SPITE_DT_F32 && x_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
@@ -524,12 +544,166 @@ SPITE_API int spite_head_norm_gate(int x_dtype, int out_dtype, const void* x, co
     cudaStream_t st = (cudaStream_t)stream;
     if (x_dtype == SPITE_DT_F32 && out_dtype == SPITE_DT_F32)
         SPITE_LAUNCH((head_norm_gate_kernel<float, float>), (int)blocks, 128, 0, st, (const float*)x, (const float*)gates,
-                     gate_stride, gain, (float*)out, n_tokens, heads, size, eps);
+                     gate_stride, gain, (float*)out, n_tokens, heads, size, eps, gate_silu, gain_per_head);
     else if (x_dtype == SPITE_DT_F32)
         SPITE_LAUNCH((head_norm_gate_kernel<float, __nv_bfloat16>), (int)blocks, 128, 0, st, (const float*)x, (const float*)gates,
-                     gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps);
+                     gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps, gate_silu, gain_per_head);
     else
         SPITE_LAUNCH((head_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16>), (int)blocks, 128, 0, st, (const __nv_bfloat16*)x,
-                     (const __nv_bfloat16*)gates, gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps);
+                     (const __nv_bfloat16*)gates, gate_stride, gain, (__nv_bfloat16*)out, n_tokens, heads, size, eps, gate_silu, gain_per_head);
+    return spite_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// out (T) = x (float32), element by element: the copy of the residual stream that a sublayer without a norm in front
+// of it reads.
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long long n4, long long n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = ((const float4*)x)[i];
+        store4(out + 4 * i, v.x, v.y, v.z, v.w);
+    }
+    if (blockIdx.x == 0)
+        for (long long i = 4 * n4 + threadIdx.x; i < n; i += blockDim.x) out[i] = from_f32<T>(x[i]);
+}
+
+SPITE_API int spite_cast_rows(int out_dtype, const float* x, void* out, long long n, void* stream) {
+    if (!x || !out || n < 0) return SPITE_BAD_ARG;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (n == 0) return SPITE_OK;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    const long long n4 = aligned ? n / 4 : 0;
+    const long long blocks = (n4 + 255) / 256;
+    const int grid = (int)(blocks < 1 ? 1 : (blocks < 4096 ? blocks : 4096));
+    if (out_dtype == SPITE_DT_F32) SPITE_LAUNCH(cast_rows_kernel<float>, grid, 256, 0, (cudaStream_t)stream, x, (float*)out, n4, n);
+    else SPITE_LAUNCH(cast_rows_kernel<__nv_bfloat16>, grid, 256, 0, (cudaStream_t)stream, x, (__nv_bfloat16*)out, n4, n);
+    return spite_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// A short causal convolution over time on every channel of a projection's output, carried from step to step:
+//     y[t, c] = act( sum_j w[c, j] * u[t - taps + 1 + j, c] ),   u = 0 before the sequence's first token
+// u is the float32 output of the projection; the last taps - 1 rows of u of every request live in its state slot
+// (float32 [taps - 1, channels], oldest first; all zeros: the start of a sequence) and are renewed by the step.
+// Columns behind the channels (`copy_columns` of them) are passed on unchanged (gate columns of the same product).
+// A thread owns one column of one block of CONV_TB tokens of one segment; only the thread of a segment's first block
+// reads or writes the slot.  Sums in float32 in the order of the taps.
+struct ShortConvParams {
+    const float* x;             // [tokens, x_stride]
+    long long x_stride;
+    const float* w;             // [channels, taps]
+    void* out;                  // [tokens, out_stride] (T or float32)
+    long long out_stride;
+    float* state;               // state + slot * slot_stride: [taps - 1, channels]
+    long long slot_stride;
+    const int* cu_seqlens;      // [segments + 1]
+    const int* slots;           // [segments]
+    int n_segments, channels, taps, copy_columns;
+    int activation;             // 0: none, 1: silu
+    int max_seg_len;
+};
+
+constexpr int CONV_TB = 16;
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128) short_conv_kernel(const ShortConvParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= p.channels + p.copy_columns) return;
+    const int s = blockIdx.y;
+    const int t0 = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - t0;
+    const int i0 = blockIdx.z * CONV_TB;
+    if (i0 >= n) return;
+    const int slot = p.slots[s];
+    // A captured step pads its rows with copies of its first row.  A copy must come out as the first row does (its
+    // keys go to the same place of the cache), but it would read a slot that the first row's thread may have renewed
+    // already: so the first row's thread writes the copies' rows as well, and the copies' threads do nothing.
+    if (s > 0 && slot == p.slots[0]) return;
+    const int i1 = min(i0 + CONV_TB, n);
+    T* out = (T*)p.out;
+    float y[CONV_TB];
+    if (c >= p.channels) {
+        for (int i = i0; i < i1; ++i) {
+            y[i - i0] = p.x[(size_t)(t0 + i) * p.x_stride + c];
+            out[(size_t)(t0 + i) * p.out_stride + c] = from_f32<T>(y[i - i0]);
+        }
+    } else {
+        const int taps = p.taps;
+        float w[CONV_MAX_TAPS], win[CONV_MAX_TAPS - 1], old[CONV_MAX_TAPS - 1];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)               // the taps right-aligned: w[CONV_MAX_TAPS - 1] is the current token's
+            w[j] = j >= CONV_MAX_TAPS - taps ? p.w[(size_t)c * taps + j - (CONV_MAX_TAPS - taps)] : 0.f;
+        float* st = p.state + (size_t)slot * p.slot_stride + c;
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) old[k] = (i0 == 0 && k < taps - 1) ? st[(size_t)k * p.channels] : 0.f;
+        // win[CONV_MAX_TAPS - 1 - d] is the input d tokens back
+#pragma unroll
+        for (int d = 1; d < CONV_MAX_TAPS; ++d) {
+            float v = 0.f;
+            if (d < taps) {
+                const int idx = i0 - d;
+                if (idx >= 0) v = p.x[(size_t)(t0 + idx) * p.x_stride + c];
+                else if (taps - 1 + idx >= 0) {
+#pragma unroll
+                    for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) if (k == taps - 1 + idx) v = old[k];
+                }
+            }
+            win[CONV_MAX_TAPS - 1 - d] = v;
+        }
+        for (int i = i0; i < i1; ++i) {
+            const float cur = p.x[(size_t)(t0 + i) * p.x_stride + c];
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) acc = fmaf(w[j], win[j], acc);
+            acc = fmaf(w[CONV_MAX_TAPS - 1], cur, acc);
+            if (p.activation == 1) acc = acc / (1.0f + expf(-acc));
+            y[i - i0] = acc;
+            out[(size_t)(t0 + i) * p.out_stride + c] = from_f32<T>(acc);
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS - 2; ++j) win[j] = win[j + 1];
+            win[CONV_MAX_TAPS - 2] = cur;
+        }
+        if (i0 == 0) {
+            // the slot's next content: the last taps - 1 inputs of the sequence so far
+            for (int k = 0; k < taps - 1; ++k) {
+                const int idx = n - (taps - 1) + k;
+                float v = 0.f;
+                if (idx >= 0) v = p.x[(size_t)(t0 + idx) * p.x_stride + c];
+                else {
+#pragma unroll
+                    for (int kk = 0; kk < CONV_MAX_TAPS - 1; ++kk) if (kk == taps - 1 + idx) v = old[kk];
+                }
+                st[(size_t)k * p.channels] = v;
+            }
+        }
+    }
+    if (s == 0 && i0 == 0) {
+        for (int s2 = 1; s2 < p.n_segments; ++s2) {
+            if (p.slots[s2] != slot) continue;
+            const int u0 = p.cu_seqlens[s2], m = min(p.cu_seqlens[s2 + 1] - u0, i1);
+            for (int i = 0; i < m; ++i) out[(size_t)(u0 + i) * p.out_stride + c] = from_f32<T>(y[i]);
+        }
+    }
+}
+
+SPITE_API int spite_short_conv(int out_dtype, const ShortConvParams* p, void* stream) {
+    if (!p || !p->x || !p->w || !p->out || !p->state || !p->cu_seqlens || !p->slots) return SPITE_BAD_ARG;
+    if (p->n_segments < 0 || p->channels < 1 || p->taps < 1 || p->copy_columns < 0 || p->max_seg_len < 0) return SPITE_BAD_ARG;
+    if (p->x_stride < p->channels + p->copy_columns || p->out_stride < p->channels + p->copy_columns) return SPITE_BAD_ARG;
+    if (p->taps > 1 && p->slot_stride < (long long)(p->taps - 1) * p->channels) return SPITE_BAD_ARG;
+    if (p->activation != 0 && p->activation != 1) return SPITE_BAD_ARG;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (p->taps > CONV_MAX_TAPS || p->n_segments > 65535) return SPITE_UNSUPPORTED;
+    if (p->n_segments == 0 || p->max_seg_len == 0) return SPITE_OK;
+    const int cols = p->channels + p->copy_columns;
+    const int zb = (p->max_seg_len + CONV_TB - 1) / CONV_TB;
+    if (zb > 65535) return SPITE_UNSUPPORTED;
+    dim3 grid((cols + 127) / 128, p->n_segments, zb);
+    if (out_dtype == SPITE_DT_F32) SPITE_LAUNCH(short_conv_kernel<float>, grid, 128, 0, (cudaStream_t)stream, *p);
+    else SPITE_LAUNCH(short_conv_kernel<__nv_bfloat16>, grid, 128, 0, (cudaStream_t)stream, *p);
     return spite_launch_status();
 }

@@ -2,7 +2,7 @@
 //
 //  * latent_prepare: one row of the first product's float32 output holds a token's query latent, its
 //    key/value latent, the key part that all heads share and the gate columns.  Both latents are RMS-normed
-//    with a gain (float32 sums and scaling), the shared key part is rotated (neighbouring pairs, angle
+//    with a gain (float32 sums and scaling), the shared key part is rotated (neighbouring pairs or halves, angle
 //    position * inv_freq[i], cos and sin times an amplitude), and the cache row of the token's position
 //    becomes [normed key/value latent ; rotated shared part ; zeros].  The gates become sigmoid(column).
 //  * latent_queries: the rotating tail of every query head is rotated the same way into the row that the
@@ -26,6 +26,7 @@ struct LatentPrepareParams {
     int num_gates;
     float* gates_out;           // [tokens, num_gates] or null
     int write_cache;
+    int pairing;                // SPITE_PAIR_*: which two elements of the shared key part pair i is
 };
 
 struct LatentQueryParams {
@@ -40,6 +41,7 @@ struct LatentQueryParams {
     int* offsets_out;           // [num_heads + 1]: offsets_out[h] = h * tokens
     void* q_sorted_out;         // [num_heads * tokens, head_dim] or null: the unrotated parts head by head (row h * tokens + t),
                                 // the order in which the product with the heads' key matrices takes its rows
+    int pairing;                // SPITE_PAIR_*: which two elements of a head's rotating tail pair i is
 };
 
 namespace {
@@ -91,7 +93,12 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const LatentPrepare
     const int first_gate = p.q_rank + p.kv_rank + p.rot_dim;
     float gate_in = 0.f, kr0 = 0.f, kr1 = 0.f;
     if (p.gates_out && (int)threadIdx.x < p.num_gates) gate_in = in[first_gate + threadIdx.x];
-    if (2 * (int)threadIdx.x < p.rot_dim) { kr0 = kr[2 * threadIdx.x]; kr1 = kr[2 * threadIdx.x + 1]; }
+    const int half_rot = p.rot_dim / 2;
+    const bool halves = p.pairing == SPITE_PAIR_HALVES;       // pair i: elements (i, i + rot_dim / 2) instead of (2i, 2i + 1)
+    if ((int)threadIdx.x < half_rot) {
+        kr0 = kr[halves ? threadIdx.x : 2 * threadIdx.x];
+        kr1 = kr[halves ? threadIdx.x + half_rot : 2 * threadIdx.x + 1];
+    }
     if (VEC) {
 #pragma unroll
         for (int r = 0; r < QV; ++r) {
@@ -146,9 +153,10 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const LatentPrepare
         float sn, cs;
         sincosf((float)pos * p.inv_freq[i], &sn, &cs);
         sn *= p.rot_amplitude; cs *= p.rot_amplitude;
-        const float a = i < (int)blockDim.x ? kr0 : kr[2 * i], bb = i < (int)blockDim.x ? kr1 : kr[2 * i + 1];
-        row[p.kv_rank + 2 * i] = from_f32<T>(a * cs - bb * sn);
-        row[p.kv_rank + 2 * i + 1] = from_f32<T>(bb * cs + a * sn);
+        const int e0 = halves ? i : 2 * i, e1 = halves ? i + half_rot : 2 * i + 1;
+        const float a = i < (int)blockDim.x ? kr0 : kr[e0], bb = i < (int)blockDim.x ? kr1 : kr[e1];
+        row[p.kv_rank + e0] = from_f32<T>(a * cs - bb * sn);
+        row[p.kv_rank + e1] = from_f32<T>(bb * cs + a * sn);
     }
     for (int i = p.kv_rank + p.rot_dim + threadIdx.x; i < c.head_dim; i += blockDim.x) row[i] = from_f32<T>(0.f);
 }
@@ -185,12 +193,20 @@ __global__ void __launch_bounds__(128) latent_queries_kernel(const LatentQueryPa
     T* out = (T*)p.q_out + (size_t)t * p.num_heads * p.row;
     for (int e = threadIdx.x; e < p.num_heads * half; e += blockDim.x) {
         const int h = e / half, i = e % half;
+        const float cs = cs_sn[i], sn = cs_sn[half + i];
+        if (p.pairing == SPITE_PAIR_HALVES) {                  // pair i: elements (i, i + rot_dim / 2)
+            const T* src = q + h * qh + p.head_dim;
+            T* dst = out + h * p.row + p.kv_rank;
+            const float a = to_f32(src[i]), bb = to_f32(src[i + half]);
+            dst[i] = from_f32<T>(a * cs - bb * sn);
+            dst[i + half] = from_f32<T>(bb * cs + a * sn);
+            continue;
+        }
         const T* src = q + h * qh + p.head_dim + 2 * i;
         T* dst = out + h * p.row + p.kv_rank + 2 * i;
         float a, bb;
         if (WIDE) load_pair(src, a, bb);
         else { a = to_f32(src[0]); bb = to_f32(src[1]); }
-        const float cs = cs_sn[i], sn = cs_sn[half + i];
         if (WIDE) store_pair(dst, a * cs - bb * sn, bb * cs + a * sn);
         else { dst[0] = from_f32<T>(a * cs - bb * sn); dst[1] = from_f32<T>(bb * cs + a * sn); }
     }
@@ -225,6 +241,7 @@ SPITE_API int spite_latent_prepare(int dtype, const LatentPrepareParams* p, cons
     if (!b->positions || !b->seg_of_token || !b->block_table || !c->kv) return SPITE_BAD_ARG;
     if (b->n_tokens < 0 || b->table_width < 1 || c->n_pages < 1 || c->page_size < 1 || c->num_kv_heads != 1) return SPITE_BAD_ARG;
     if (p->q_rank < 1 || p->kv_rank < 1 || p->rot_dim < 2 || p->rot_dim % 2 || p->num_gates < 0) return SPITE_BAD_ARG;
+    if (p->pairing != SPITE_PAIR_NEIGHBOURS && p->pairing != SPITE_PAIR_HALVES) return SPITE_BAD_ARG;
     if (p->gates_out ? p->num_gates < 1 : false) return SPITE_BAD_ARG;
     if (p->down_stride < (long long)p->q_rank + p->kv_rank + p->rot_dim + (p->gates_out ? p->num_gates : 0)) return SPITE_BAD_ARG;
     if (c->head_dim < p->kv_rank + p->rot_dim) return SPITE_BAD_ARG;
@@ -249,6 +266,7 @@ SPITE_API int spite_latent_queries(int dtype, const LatentQueryParams* p, void* 
     if (!p || !p->q || !p->q_out || !p->inv_freq || !p->positions || !p->rows_out || !p->offsets_out) return SPITE_BAD_ARG;
     if (p->num_heads < 1 || p->head_dim < 1 || p->kv_rank < 1 || p->rot_dim < 2 || p->rot_dim % 2 || p->n_tokens < 0) return SPITE_BAD_ARG;
     if (p->row < p->kv_rank + p->rot_dim) return SPITE_BAD_ARG;
+    if (p->pairing != SPITE_PAIR_NEIGHBOURS && p->pairing != SPITE_PAIR_HALVES) return SPITE_BAD_ARG;
     if (p->rot_dim > 8192) return SPITE_UNSUPPORTED;
     if (p->n_tokens == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;

@@ -6,6 +6,8 @@
 //   (moe.rs:120).  No softmax, no renormalisation.  A second scoring rule, SCORE_SOFTMAX_RENORM: the weight
 //   of a choice is its share of the softmax over all experts divided by the sum of the chosen shares
 //   (+ 1e-20), all float32; the order of the experts is the same (the softmax is monotonic).
+//   A third, SCORE_SOFTMAX_BIASED: the experts are ordered by their softmax share plus a per-expert constant
+//   (`choice_bias`), and the weight of a choice is its share alone, not renormalised.
 //   Choices are stored slot-major: expert_ids[slot][token], weights[slot][token].
 // sort: for every choice slot a stable counting sort of the tokens by expert:
 //   offsets[slot][e] .. offsets[slot][e+1] are the places of expert e's tokens in
@@ -25,7 +27,7 @@ constexpr int MAX_EXPERTS = 1024;
 constexpr int TB = 8;                  // tokens per block of the logits kernel
 constexpr int EB = 2;                  // experts per block
 constexpr int WARPS = 8;
-constexpr int SCORE_SIGMOID = 0, SCORE_SOFTMAX_RENORM = 1;
+constexpr int SCORE_SIGMOID = 0, SCORE_SOFTMAX_RENORM = 1, SCORE_SOFTMAX_BIASED = 2;
 
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
     const float4 t = *(const float4*)p;
@@ -121,7 +123,8 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
                                                                int* __restrict__ expert_ids, float* __restrict__ weights,
                                                                int* __restrict__ offsets,
                                                                int* __restrict__ sorted_rows, int scoring,
-                                                               float* __restrict__ sorted_weights) {
+                                                               float* __restrict__ sorted_weights,
+                                                               const float* __restrict__ choice_bias) {
     __shared__ int counts[MAX_EXPERTS + 1];
     pdl_wait();
     pdl_launch_dependents();
@@ -133,6 +136,30 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
     for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
         // the slot-th element in the order (logit descending, expert id ascending)
         const float* l = logits + (size_t)t * n_experts;
+        if (scoring == SCORE_SOFTMAX_BIASED) {
+            // share_e = exp(l_e - max) / Z; the slot-th expert in the order (share + bias descending, expert id ascending)
+            float mx = -INFINITY, z = 0.f;
+            for (int e = 0; e < n_experts; ++e) mx = fmaxf(mx, l[e]);
+            for (int e = 0; e < n_experts; ++e) z += expf(l[e] - mx);
+            float pv = INFINITY, bv = 0.f;
+            int pe = -1, be = 0;
+            for (int s = 0; s <= slot; ++s) {
+                bv = -INFINITY;
+                be = -1;
+                for (int e = 0; e < n_experts; ++e) {
+                    const float v = expf(l[e] - mx) / z + choice_bias[e];
+                    const bool after_prev = v < pv || (v == pv && e > pe);
+                    if (after_prev && (be < 0 || v > bv)) { bv = v; be = e; }
+                }
+                if (be < 0) { be = 0; bv = 0.f; }
+                pv = bv;
+                pe = be;
+            }
+            ids[t] = be;
+            weights[(size_t)slot * n_tokens + t] = expf(l[be] - mx) / z;
+            atomicAdd(&counts[be + 1], 1);
+            continue;
+        }
         float prev_v = INFINITY;
         int prev_e = -1;
         float best_v = 0.f, mine_v = 0.f;
@@ -197,9 +224,10 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
 SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, int n_tokens, int d,
                               int n_experts, int top_k, int* expert_ids, float* weights,
                               float* logits, int* offsets, int* sorted_rows, int scoring, float* sorted_weights,
-                              void* stream) {
+                              const float* choice_bias, void* stream) {
     if (!x || !w_router || !expert_ids || !weights || !logits || !offsets || !sorted_rows) return SPITE_BAD_ARG;
-    if (scoring != SCORE_SIGMOID && scoring != SCORE_SOFTMAX_RENORM) return SPITE_BAD_ARG;
+    if (scoring != SCORE_SIGMOID && scoring != SCORE_SOFTMAX_RENORM && scoring != SCORE_SOFTMAX_BIASED) return SPITE_BAD_ARG;
+    if (scoring == SCORE_SOFTMAX_BIASED && !choice_bias) return SPITE_BAD_ARG;
     if (n_tokens < 0 || d <= 0 || n_experts < 1 || top_k < 1 || top_k > n_experts) return SPITE_BAD_ARG;
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
@@ -220,6 +248,58 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
     }
     SPITE_LAUNCH(select_and_sort_kernel, top_k, 1024, 0, st, (const float*)logits, n_tokens, n_experts, top_k,
-                 expert_ids, weights, offsets, sorted_rows, scoring, sorted_weights);
+                 expert_ids, weights, offsets, sorted_rows, scoring, sorted_weights, choice_bias);
+    return spite_launch_status();
+}
+
+namespace {
+
+// Experts that return their input: out[t, :] (=|+=) sum over the choice slots whose expert id is `first_identity` or
+// above of weights[slot][t] * x[t, :], the slots in ascending order.  With `accumulate` 0 every row of `out` is written
+// (zeros where no such expert was chosen), so the kernel also starts the sum that the real experts then add to.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_identity_kernel(const T* __restrict__ x, const int* __restrict__ expert_ids,
+                                                           const float* __restrict__ weights, int n_tokens, int d, int top_k,
+                                                           int first_identity, float* __restrict__ out, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    float w = 0.f;
+    bool any = false;
+    for (int s = 0; s < top_k; ++s)
+        if (expert_ids[(size_t)s * n_tokens + t] >= first_identity) { w += weights[(size_t)s * n_tokens + t]; any = true; }
+    if (!any && accumulate) return;
+    const T* in = x + (size_t)t * d;
+    float* o = out + (size_t)t * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        // (the slots' terms are weights times the same element: their sum is the element times the sum of the weights,
+        // added slot by slot so that one identity expert gives w * x exactly)
+        float v = 0.f;
+        if (any) {
+            const float xv = to_f32(in[c]);
+            for (int s = 0; s < top_k; ++s)
+                if (expert_ids[(size_t)s * n_tokens + t] >= first_identity) v = fmaf(weights[(size_t)s * n_tokens + t], xv, v);
+        }
+        o[c] = accumulate ? o[c] + v : v;
+    }
+    (void)w;
+}
+
+}  // namespace
+
+SPITE_API int spite_moe_identity(int dtype, const void* x, const int* expert_ids, const float* weights, int n_tokens, int d,
+                                 int top_k, int first_identity, float* out, int accumulate, void* stream) {
+    if (!x || !expert_ids || !weights || !out) return SPITE_BAD_ARG;
+    if (n_tokens < 0 || d <= 0 || top_k < 1 || first_identity < 0) return SPITE_BAD_ARG;
+    if (dtype != SPITE_DT_F32 && dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (n_tokens == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == SPITE_DT_F32)
+        SPITE_LAUNCH(moe_identity_kernel<float>, n_tokens, threads, 0, st, (const float*)x, expert_ids, weights, n_tokens, d, top_k,
+                     first_identity, out, accumulate);
+    else
+        SPITE_LAUNCH(moe_identity_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)x, expert_ids, weights,
+                     n_tokens, d, top_k, first_identity, out, accumulate);
     return spite_launch_status();
 }

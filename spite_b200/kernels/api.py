@@ -72,19 +72,34 @@ class KernelSet:
     def rms_norm_residual(self, y, gain, eps, mult, h, *, next_gain=None, next_out=None):
         """A sublayer's output is normed before it joins the residual stream:
         h[m, :] += mult * y[m, :] * rsqrt(mean(y[m]^2) + eps) * gain (y, h float32 [M, d]); with `next_out` [M, d]
-        (T) also the norm the next sublayer reads, of the row just made: next_out = h * rsqrt(mean(h^2) + eps) * next_gain."""
+        (T) also the norm the next sublayer reads, of the row just made: next_out = h * rsqrt(mean(h^2) + eps) * next_gain;
+        `next_out` without `next_gain`: the row itself in next_out's type (the next sublayer reads the stream unnormed)."""
+        raise NotImplementedError
+
+    def cast_rows(self, h, out):
+        """out (T) = h (float32), element by element: what a sublayer without a norm in front of it reads."""
+        raise NotImplementedError
+
+    def short_conv(self, x, w, out, batch, state, *, channels, activation=None, state_offset=0):
+        """A short causal convolution over time on the first `channels` columns of a projection's float32 output x
+        [M, >= channels + c]: out[t, ch] = act(sum_j w[ch, j] * x[t - taps + 1 + j, ch]) within each segment, w float32
+        [channels, taps]; rows before a segment's first token come from the request's slot, state[slot, state_offset :
+        state_offset + (taps - 1) * channels] (float32 [taps - 1, channels], oldest first; zeros at the start of a
+        sequence), which then receives the sequence's last taps - 1 rows of x.  The c = out.shape[1] - channels columns behind
+        the channels are passed on unchanged.  out [M, channels + c] is T or float32; `activation` None or "silu"."""
         raise NotImplementedError
 
     def fill_rows(self, out, vec, *, accumulate=False):
         """out[m, :] (float32 [M, d]) = vec (float32 [d]), or += vec: a bias laid down for a product that adds to it."""
         raise NotImplementedError
 
-    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None, gate_activation="sigmoid"):
         """What stands between a mixer's heads and its output projection.  x [M, heads * size] (T, or float32: the
         result of a recurrence), out [M, heads * size] (T; may be x):
         out[m, h, j] = x[m, h, j] * r * gain[h * size + j] * sigmoid(gates[m, gate_column + h * size + j]) with
         r = rsqrt(mean_j x[m, h, :]^2 + eps) if `eps` is given (a norm of every head without a gain of its own), else 1;
-        `gates` (a 2-D tensor of x's type, the gate columns of a wider product) and `gain` (float32) may be left out."""
+        `gates` (a 2-D tensor of x's type, the gate columns of a wider product) and `gain` (float32) may be left out.
+        `gate_activation` "silu": the factor is z * sigmoid(z) of the gate column z instead of sigmoid(z)."""
         raise NotImplementedError
 
     # ---- matrix products: y = x W^T with W [out, in]
@@ -130,7 +145,7 @@ class KernelSet:
 
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None, bias=None, q_only=False):
+                   value_mix=None, gates_out=None, bias=None, q_only=False, norm_dim=None):
         """Encode positions of q and k, normalise, scale q, append k and v to the cache.
         `bias` float32 [(nq + 2 nkv) hd]: added to the projection's columns before anything else.  `q_only`: a row of
         qkv holds the q heads alone (and `bias` theirs): the layer reads keys and values that another layer cached.
@@ -140,12 +155,16 @@ class KernelSet:
         (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1.
         `value_mix` = (other [M, *] T, column, head stride, value size, lam): element i < value size of kv head g's
         value becomes (1 - lam) v + lam * other[m, column + g * head stride + i] before it is cached.
-        `gates_out` float32 [M, nq]: receives sigmoid(qkv[m, (nq + 2 nkv) hd + h]), the columns after the heads."""
+        `gates_out` float32 [M, nq]: receives sigmoid(qkv[m, (nq + 2 nkv) hd + h]), the columns after the heads.
+        `norm_dim`: a q or k head has this many elements and zeros behind them up to hd (a cache row wider than the key):
+        the per-head norm takes its mean over them."""
         raise NotImplementedError
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False,
+                        score_softcap=None):
         """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V.
+        `score_softcap` c: a scaled score s becomes c * tanh(s / c) before anything else happens to it.
         `out_by_head`: the result is laid out head by head instead, out[nq, M, hd] (the order in which a product per
         head reads its rows).
         `sink_logit`: the softmax's denominator also holds exp(sink_logit), a key without a value;
@@ -164,7 +183,7 @@ class KernelSet:
         """One row of `down` (float32 [M, >= q_rank + kv_rank + rot + num_gates]) holds a token's query latent, its
         key/value latent, the key part that all heads share and the gate columns.  cq_out [M, q_rank] (T) =
         RMS norm of the query latent * q_gain; the cache row of the token's position becomes [RMS norm of the
-        key/value latent * kv_gain; the shared part rotated by `rotation` (neighbouring pairs, times its amplitude);
+        key/value latent * kv_gain; the shared part rotated by `rotation` (either pairing, times its amplitude);
         zeros up to the row's size]; gates_out [M, num_gates] float32 = sigmoid of the gate columns."""
         raise NotImplementedError
 
@@ -197,12 +216,32 @@ class KernelSet:
         rounded up to a multiple of four floats."""
         return dim * vdim + -(-vdim // 32) * (-(-(dim + 1) // 4) * 4)
 
+    def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
+                   unit_eps=1e-6, state_offset=0):
+        """The gated delta rule, token by token, for every segment of the step from the matrix its request's slot holds
+        (zeros: the start of a sequence); the slot receives the matrix after the segment's last token.  x float32 [M, *]
+        holds, from the columns `columns` = (q, k, v, b, a) on, q and k [kv_heads * dim], v [heads * vdim] and two
+        numbers a head; out float32 [M, heads * vdim]; state float32 [slots, *], head h's S [dim, vdim] row-major at
+        state[slot, state_offset + h * dim * vdim].  Head h reads q/k head h // (heads / kv_heads).
+        k <- k / sqrt(|k|^2 + unit_eps), q <- q / sqrt(|q|^2 + unit_eps) * q_scale, beta = sigmoid(b),
+        g = exp(-exp(a_log[h]) * softplus(a + dt_bias[h])); S <- g S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.
+        All float32."""
+        raise NotImplementedError
+
     # ---- mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
+    def moe_identity(self, x, routing, first_identity, out, *, accumulate=True):
+        """Experts that return their input: out[m, :] (float32) (+)= sum over the choice slots s whose expert id
+        routing.expert_ids[s, m] >= first_identity of routing.weights[s, m] * x[m, :] (x is T).  Without `accumulate`
+        every row of out is written (zeros where no such expert was chosen)."""
+        raise NotImplementedError
+
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid", choice_bias=None) -> Routing:
         """Router logits in float32, the `top_k` largest per token (equal ones: the lower expert first), the
         tokens sorted by expert for every choice slot.  `scoring` "sigmoid": the weight of a choice is the sigmoid
         of its logit; "softmax_renorm": its share of the softmax over all experts, divided by the sum of the
-        chosen shares (+ 1e-20); `sorted_weights` is filled for it."""
+        chosen shares (+ 1e-20); `sorted_weights` is filled for it.  "softmax_biased": the experts are ordered by their
+        softmax share plus `choice_bias` (float32 [E]), and the weight of a choice is its share alone (not renormalised);
+        `sorted_weights` is filled."""
         raise NotImplementedError
 
     # ---- sampling

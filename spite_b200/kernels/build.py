@@ -41,6 +41,7 @@ LIBRARIES = {
     "moe": (["moe.cu"], []),
     "latent": (["latent.cu"], []),
     "recurrent": (["recurrent.cu"], []),
+    "delta": (["delta.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

@@ -51,7 +51,7 @@ class QkPrepareParams(C.Structure):
                 ("qkv_stride", C.c_longlong), ("rot_amplitude", C.c_float),
                 ("v_other", C.c_void_p), ("v_other_stride", C.c_longlong), ("v_other_head", C.c_int),
                 ("v_mix_dim", C.c_int), ("v_mix", C.c_float), ("gates_out", C.c_void_p),
-                ("bias", C.c_void_p), ("q_only", C.c_int)]
+                ("bias", C.c_void_p), ("q_only", C.c_int), ("norm_dim", C.c_int)]
 
 
 class AttentionParams(C.Structure):
@@ -59,7 +59,7 @@ class AttentionParams(C.Structure):
                 ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float),
                 ("has_sink", C.c_int), ("sink_logit", C.c_float),
                 ("head_sinks", C.c_void_p), ("head_slopes", C.c_void_p), ("head_gates", C.c_void_p),
-                ("out_by_head_tokens", C.c_int)]
+                ("out_by_head_tokens", C.c_int), ("score_softcap", C.c_float)]
 
 
 class LatentPrepareParams(C.Structure):
@@ -67,14 +67,30 @@ class LatentPrepareParams(C.Structure):
                 ("q_gain", C.c_void_p), ("kv_gain", C.c_void_p), ("inv_freq", C.c_void_p),
                 ("rot_amplitude", C.c_float), ("eps", C.c_float),
                 ("q_rank", C.c_int), ("kv_rank", C.c_int), ("rot_dim", C.c_int), ("num_gates", C.c_int),
-                ("gates_out", C.c_void_p), ("write_cache", C.c_int)]
+                ("gates_out", C.c_void_p), ("write_cache", C.c_int), ("pairing", C.c_int)]
 
 
 class LatentQueryParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("q_out", C.c_void_p), ("inv_freq", C.c_void_p), ("rot_amplitude", C.c_float),
                 ("num_heads", C.c_int), ("head_dim", C.c_int), ("rot_dim", C.c_int), ("kv_rank", C.c_int),
                 ("row", C.c_int), ("positions", C.c_void_p), ("n_tokens", C.c_int),
-                ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p), ("q_sorted_out", C.c_void_p)]
+                ("rows_out", C.c_void_p), ("offsets_out", C.c_void_p), ("q_sorted_out", C.c_void_p), ("pairing", C.c_int)]
+
+
+class ShortConvParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_stride", C.c_longlong), ("w", C.c_void_p), ("out", C.c_void_p),
+                ("out_stride", C.c_longlong), ("state", C.c_void_p), ("slot_stride", C.c_longlong),
+                ("cu_seqlens", C.c_void_p), ("slots", C.c_void_p), ("n_segments", C.c_int), ("channels", C.c_int),
+                ("taps", C.c_int), ("copy_columns", C.c_int), ("activation", C.c_int), ("max_seg_len", C.c_int)]
+
+
+class DeltaParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("stride", C.c_longlong),
+                ("q_col", C.c_int), ("k_col", C.c_int), ("v_col", C.c_int), ("b_col", C.c_int), ("a_col", C.c_int),
+                ("a_log", C.c_void_p), ("dt_bias", C.c_void_p), ("out", C.c_void_p), ("state", C.c_void_p),
+                ("slot_stride", C.c_longlong), ("cu_seqlens", C.c_void_p), ("slots", C.c_void_p),
+                ("n_segments", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
+                ("q_scale", C.c_float), ("unit_eps", C.c_float)]
 
 
 class MlstmParams(C.Structure):
@@ -365,11 +381,13 @@ class CudaKernels(KernelSet):
         M, d = h.shape
         if tuple(y.shape) != (M, d) or gain.numel() != d:
             raise KernelError("rms_norm_residual: shapes do not fit")
-        if (next_out is None) != (next_gain is None):
-            raise KernelError("rms_norm_residual: the next norm needs its gain and its output")
+        if next_gain is not None and next_out is None:
+            raise KernelError("rms_norm_residual: the next norm needs its output")
         if next_out is not None:
-            self._t(next_out, None, "next_out"); self._t(next_gain, torch.float32, "next_gain")
-            if tuple(next_out.shape) != (M, d) or next_gain.numel() != d or next_out.dtype not in _DT:
+            self._t(next_out, None, "next_out")
+            if next_gain is not None:
+                self._t(next_gain, torch.float32, "next_gain")
+            if tuple(next_out.shape) != (M, d) or (next_gain is not None and next_gain.numel() != d) or next_out.dtype not in _DT:
                 raise KernelError("rms_norm_residual: the next norm's output or gain does not fit")
         st = self._lib("elementwise").spite_rms_norm_residual(
             _DT[next_out.dtype] if next_out is not None else self._dt, C.c_void_p(y.data_ptr()), C.c_void_p(gain.data_ptr()),
@@ -377,6 +395,39 @@ class CudaKernels(KernelSet):
             C.c_float(mult), self._stream())
         self._count("elementwise", 1)
         _check(st, "rms_norm_residual")
+
+    def cast_rows(self, h, out):
+        self._t(h, torch.float32, "h"); self._t(out, self.dtype, "out")
+        if out.numel() != h.numel():
+            raise KernelError("cast_rows: out must have as many elements as h")
+        st = self._lib("elementwise").spite_cast_rows(self._dt, C.c_void_p(h.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                      C.c_longlong(h.numel()), self._stream())
+        self._count("elementwise", 1)
+        _check(st, "cast_rows")
+
+    def short_conv(self, x, w, out, batch, state, *, channels, activation=None, state_offset=0):
+        self._t(x, torch.float32, "x"); self._t(w, torch.float32, "w"); self._t(out, None, "out")
+        self._t(state, torch.float32, "state")
+        if out.dtype not in (self.dtype, torch.float32):
+            raise KernelError(f"short_conv: out must be {self.dtype} or float32")
+        M = x.shape[0]
+        taps = w.shape[1]
+        if w.shape[0] != channels or out.shape[0] != M or out.shape[1] < channels or x.shape[1] < out.shape[1]:
+            raise KernelError("short_conv: shapes do not fit")
+        if activation not in (None, "silu"):
+            raise KernelError(f"short_conv: unknown activation {activation!r}")
+        slot_stride = state[0].numel()
+        if state_offset < 0 or state_offset + (taps - 1) * channels > slot_stride:
+            raise KernelError("short_conv: the slot cannot hold the convolution's rows")
+        n_seg = batch.cu_seqlens.numel() - 1
+        p = ShortConvParams(x=x.data_ptr(), x_stride=x.shape[1], w=w.data_ptr(), out=out.data_ptr(), out_stride=out.shape[1],
+                            state=state.data_ptr() + 4 * int(state_offset), slot_stride=slot_stride,
+                            cu_seqlens=batch.cu_seqlens.data_ptr(), slots=batch.slots.data_ptr(), n_segments=n_seg,
+                            channels=int(channels), taps=int(taps), copy_columns=out.shape[1] - int(channels),
+                            activation=1 if activation == "silu" else 0, max_seg_len=int(batch.max_seg_len))
+        st = self._lib("elementwise").spite_short_conv(_DT[out.dtype], C.byref(p), self._stream())
+        self._count("elementwise", 1)
+        _check(st, "short_conv")
 
     def fill_rows(self, out, vec, *, accumulate=False):
         self._t(out, torch.float32, "out"); self._t(vec, torch.float32, "vec")
@@ -388,8 +439,10 @@ class CudaKernels(KernelSet):
         self._count("elementwise", 1)
         _check(st, "fill_rows")
 
-    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None, gate_activation="sigmoid"):
         self._t(x, None, "x"); self._t(out, self.dtype, "out")
+        if gate_activation not in ("sigmoid", "silu"):
+            raise KernelError(f"head_norm_gate: unknown gate activation {gate_activation!r}")
         if x.dtype not in (self.dtype, torch.float32):
             raise KernelError(f"head_norm_gate: x must be {self.dtype} or float32")
         M = x.shape[0]
@@ -406,7 +459,7 @@ class CudaKernels(KernelSet):
         st = self._lib("elementwise").spite_head_norm_gate(
             _DT[x.dtype], self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(g_ptr), C.c_longlong(g_stride),
             C.c_void_p(_ptr(gain)), C.c_void_p(out.data_ptr()), M, int(heads), int(size), C.c_float(eps or 0.0),
-            self._stream())
+            int(gate_activation == "silu"), 1, self._stream())
         self._count("elementwise", 1)
         _check(st, "head_norm_gate")
 
@@ -679,7 +732,7 @@ class CudaKernels(KernelSet):
                           page_size=kv.shape[3], num_kv_heads=kv.shape[2], head_dim=kv.shape[4])
 
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None, bias=None, q_only=False):
+                   value_mix=None, gates_out=None, bias=None, q_only=False, norm_dim=None):
         self._t(qkv, self.dtype, "qkv"); self._t(q_out, self.dtype, "q_out")
         head_dim = cache.kv.shape[4]
         n_cols = (num_heads + (0 if q_only else 2 * cache.kv.shape[2])) * head_dim
@@ -724,7 +777,8 @@ class CudaKernels(KernelSet):
                             temperature_floor=floor, temperature_scale=scale, num_heads=num_heads,
                             write_cache=int(cache.write), qkv_stride=qkv.shape[1], rot_amplitude=amplitude,
                             v_other=v_other, v_other_stride=v_stride, v_other_head=int(v_head), v_mix_dim=int(v_dim),
-                            v_mix=float(v_lam), gates_out=_ptr(gates_out), bias=_ptr(bias), q_only=int(bool(q_only)))
+                            v_mix=float(v_lam), gates_out=_ptr(gates_out), bias=_ptr(bias), q_only=int(bool(q_only)),
+                            norm_dim=int(norm_dim or 0))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
         self._count("attention", 1)
@@ -732,8 +786,11 @@ class CudaKernels(KernelSet):
 
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False,
+                        score_softcap=None):
         self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
+        if score_softcap is not None and not score_softcap > 0:
+            raise KernelError("paged_attention: the cap of the scores must be positive")
         if out.numel() != q.numel():
             raise KernelError("paged_attention: out must have as many elements as q")
         for name, t, n in (("head_sinks", head_sinks, num_heads), ("head_slopes", head_slopes, num_heads),
@@ -748,7 +805,7 @@ class CudaKernels(KernelSet):
                             has_sink=int(sink_logit is not None or head_sinks is not None),
                             sink_logit=float(sink_logit or 0.0), head_sinks=_ptr(head_sinks),
                             head_slopes=_ptr(head_slopes), head_gates=_ptr(head_gates),
-                            out_by_head_tokens=q.shape[0] if out_by_head else 0)
+                            out_by_head_tokens=q.shape[0] if out_by_head else 0, score_softcap=float(score_softcap or 0.0))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         group = num_heads // c.num_kv_heads
         if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16
@@ -870,8 +927,6 @@ class CudaKernels(KernelSet):
         self._t(down, torch.float32, "down"); self._t(cq_out, self.dtype, "cq_out")
         self._t(q_gain, torch.float32, "q_gain"); self._t(kv_gain, torch.float32, "kv_gain")
         inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
-        if rotation.pairing != "neighbours":
-            raise KernelError("latent_prepare rotates neighbouring pairs")
         if q_gain.numel() != q_rank or kv_gain.numel() != kv_rank or tuple(cq_out.shape) != (down.shape[0], q_rank):
             raise KernelError("latent_prepare: shapes do not fit")
         if cache.kv.shape[0] != 1:
@@ -882,7 +937,8 @@ class CudaKernels(KernelSet):
                                 q_gain=q_gain.data_ptr(), kv_gain=kv_gain.data_ptr(), inv_freq=inv_freq.data_ptr(),
                                 rot_amplitude=float(rotation.amplitude), eps=float(eps), q_rank=int(q_rank),
                                 kv_rank=int(kv_rank), rot_dim=2 * inv_freq.numel(), num_gates=int(num_gates),
-                                gates_out=_ptr(gates_out), write_cache=int(cache.write))
+                                gates_out=_ptr(gates_out), write_cache=int(cache.write),
+                                pairing={"neighbours": 0, "halves": 1}[rotation.pairing])
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("latent").spite_latent_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
         self._count("latent", 1)
@@ -903,7 +959,8 @@ class CudaKernels(KernelSet):
                               rot_amplitude=float(rotation.amplitude), num_heads=int(num_heads), head_dim=int(head_dim),
                               rot_dim=rot, kv_rank=int(kv_rank), row=q_out.shape[1] // num_heads,
                               positions=batch.positions.data_ptr(), n_tokens=M, rows_out=rows_out.data_ptr(),
-                              offsets_out=offsets_out.data_ptr(), q_sorted_out=_ptr(sorted_out))
+                              offsets_out=offsets_out.data_ptr(), q_sorted_out=_ptr(sorted_out),
+                              pairing={"neighbours": 0, "halves": 1}[rotation.pairing])
         st = self._lib("latent").spite_latent_queries(self._dt, C.byref(p), self._stream())
         self._count("latent", 1)
         _check(st, "latent_queries")
@@ -941,10 +998,48 @@ class CudaKernels(KernelSet):
         self._count("recurrent", 2 if chunked else 1)
         _check(st, "mlstm_scan")
 
+    def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
+                   unit_eps=1e-6, state_offset=0):
+        self._t(x, torch.float32, "x"); self._t(out, torch.float32, "out"); self._t(state, torch.float32, "state")
+        self._t(a_log, torch.float32, "a_log"); self._t(dt_bias, torch.float32, "dt_bias")
+        M = x.shape[0]
+        q_col, k_col, v_col, b_col, a_col = (int(c) for c in columns)
+        slot_stride = state[0].numel()
+        if tuple(out.shape) != (M, heads * vdim) or a_log.numel() != heads or dt_bias.numel() != heads or heads % kv_heads \
+                or state_offset < 0 or state_offset + heads * dim * vdim > slot_stride:
+            raise KernelError("delta_scan: shapes do not fit")
+        if max(q_col + kv_heads * dim, k_col + kv_heads * dim, v_col + heads * vdim, b_col + heads, a_col + heads) > x.shape[1]:
+            raise KernelError("delta_scan: the columns lie outside the rows of x")
+        p = DeltaParams(x=x.data_ptr(), stride=x.shape[1], q_col=q_col, k_col=k_col, v_col=v_col, b_col=b_col, a_col=a_col,
+                        a_log=a_log.data_ptr(), dt_bias=dt_bias.data_ptr(), out=out.data_ptr(),
+                        state=state.data_ptr() + 4 * int(state_offset), slot_stride=slot_stride,
+                        cu_seqlens=batch.cu_seqlens.data_ptr(), slots=batch.slots.data_ptr(),
+                        n_segments=batch.cu_seqlens.numel() - 1, heads=int(heads), kv_heads=int(kv_heads), dim=int(dim),
+                        vdim=int(vdim), q_scale=float(q_scale), unit_eps=float(unit_eps))
+        st = self._lib("delta").spite_delta_scan(C.byref(p), self._stream())
+        self._count("delta", 1)
+        _check(st, "delta_scan")
+
     # ------------------------------------------------------------------ mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
-        if scoring not in ("sigmoid", "softmax_renorm"):
+    def moe_identity(self, x, routing, first_identity, out, *, accumulate=True):
+        self._t(x, self.dtype, "x"); self._t(out, torch.float32, "out")
+        M, d = x.shape
+        top_k = routing.expert_ids.shape[0]
+        if tuple(out.shape) != (M, d) or routing.expert_ids.shape[1] != M or tuple(routing.weights.shape) != (top_k, M):
+            raise KernelError("moe_identity: shapes do not fit")
+        st = self._lib("moe").spite_moe_identity(
+            self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(routing.expert_ids.data_ptr()), C.c_void_p(routing.weights.data_ptr()),
+            M, d, top_k, int(first_identity), C.c_void_p(out.data_ptr()), int(bool(accumulate)), self._stream())
+        self._count("moe", 1)
+        _check(st, "moe_identity")
+
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid", choice_bias=None) -> Routing:
+        if scoring not in ("sigmoid", "softmax_renorm", "softmax_biased"):
             raise KernelError(f"moe_route: unknown scoring {scoring!r}")
+        if (scoring == "softmax_biased") != (choice_bias is not None):
+            raise KernelError("moe_route: `choice_bias` goes with the scoring 'softmax_biased'")
+        if choice_bias is not None and self._t(choice_bias, torch.float32, "choice_bias").numel() != w_router.shape[0]:
+            raise KernelError("moe_route: one choice bias per expert")
         self._t(x, self.dtype, "x"); self._t(w_router, torch.float32, "w_router")
         M, d = x.shape
         E = w_router.shape[0]
@@ -954,13 +1049,13 @@ class CudaKernels(KernelSet):
         offsets = torch.empty((top_k, E + 1), dtype=torch.int32, device=dev)
         rows = torch.empty((top_k, M), dtype=torch.int32, device=dev)
         logits = torch.empty((M, E), dtype=torch.float32, device=dev)
-        renorm = scoring == "softmax_renorm"
+        renorm = {"sigmoid": 0, "softmax_renorm": 1, "softmax_biased": 2}[scoring]
         sorted_w = torch.empty((top_k, M), dtype=torch.float32, device=dev) if renorm else None
         st = self._lib("moe").spite_moe_route(
             self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
             C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
             C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), int(renorm), C.c_void_p(_ptr(sorted_w)),
-            self._stream())
+            C.c_void_p(_ptr(choice_bias)), self._stream())
         self._count("moe", 2)
         _check(st, "moe_route")
         return Routing(ids, wts, offsets, rows, logits if want_logits else None, sorted_w)

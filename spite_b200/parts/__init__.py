@@ -1,7 +1,7 @@
 from .base import (Block, BuildContext, FeedForward, Junction, Mixer, Norm, ParamSpec, Part, PositionEncoding, QkNorm,
                    Rotation, build_part, register_block, register_feed_forward, register_junction, register_mixer,
                    register_norm, register_position, registered)
-from . import norm, position, attention, latent, mlstm, feedforward, block, junction  # noqa: F401  (register the built-in parts)
+from . import norm, position, attention, latent, mlstm, delta, feedforward, block, junction  # noqa: F401  (register the built-in parts)
 
 __all__ = ["Block", "BuildContext", "FeedForward", "Junction", "Mixer", "Norm", "ParamSpec", "Part",
            "PositionEncoding", "QkNorm", "Rotation", "build_part", "register_block", "register_feed_forward",

@@ -21,7 +21,7 @@ import math
 
 import torch
 
-from ..cache import PagedKV, Window
+from ..cache import FixedState, PagedKV, Window
 from ..config.specs import ConfigError, PartSpec
 from .base import Mixer, ParamSpec, QkNorm, build_part, register_mixer
 
@@ -36,7 +36,7 @@ class PagedAttention(Mixer):
                  position: PartSpec, window=("full", 0), qk_norm_eps=None, qk_norm_gain=False,
                  qk_norm_before_rotation=False, temperature_tuning=None, softmax_scale=None,
                  value_dim=None, sink_logit=None, head_sinks=False, distance_slopes=None, head_gate=False,
-                 value_mix=None, bias=False, output_gate=False, kv_shared=False):
+                 value_mix=None, bias=False, output_gate=False, kv_shared=False, conv_taps=None, score_softcap=None):
         """`head_dim` is the size of a query and a key head, `value_dim` that of a value head (default: the
         same).  `sink_logit`, if given, is the score of a sink: a term exp(sink) in every softmax's sum that adds
         nothing to the output, p_j = exp(s_j) / (exp(sink) + sum exp(s_j')); with `head_sinks` the score is a
@@ -49,8 +49,20 @@ class PagedAttention(Mixer):
         `o_bias`).  `output_gate`: the concatenated heads are multiplied element by element by sigmoid(W x), W the
         parameter `out_gate_proj` [heads * value size, hidden], x the mixer's input, before the output projection.
         `kv_shared`: the layer has no key and value projections; it reads the cache another layer of the run order
-        writes (keys after that layer's rotation) with its own queries, window and everything else."""
+        writes (keys after that layer's rotation) with its own queries, window and everything else.
+        `conv_taps` n: q, k and v pass a causal convolution over time of n taps per channel (`q_conv`, `k_conv`, `v_conv`
+        [channels, n], the last column the current token's) directly behind their projections, before norm and
+        rotation; a request's last n - 1 projected rows are kept in its state slot.  `score_softcap` c: a scaled score s
+        becomes c tanh(s / c) before the softmax."""
         super().__init__(ctx)
+        self.conv_taps = None if conv_taps is None else int(conv_taps)
+        if self.conv_taps is not None and (self.conv_taps < 1 or self.conv_taps > 8):
+            raise ConfigError(f"conv_taps {conv_taps} must lie in 1..8")
+        if self.conv_taps is not None and kv_shared:
+            raise ConfigError("a layer that reads another layer's keys and values keeps no convolution state of its own")
+        self.score_softcap = None if score_softcap is None else float(score_softcap)
+        if self.score_softcap is not None and not self.score_softcap > 0:
+            raise ConfigError("score_softcap must be positive")
         self.has_bias, self.output_gate, self.kv_shared = bool(bias), bool(output_gate), bool(kv_shared)
         if self.kv_shared and value_mix:
             raise ConfigError("a layer that reads another layer's keys and values has no values to blend")
@@ -90,7 +102,8 @@ class PagedAttention(Mixer):
         rot = self.position.rotation()
         if rot is not None and (rot.rotary_dim or self.kd) > self.kd:
             raise ConfigError(f"{rot.rotary_dim} rotating elements in a head of {self.kd}")
-        may_pad = qk_norm_eps is None and (rot is None or rot.rotary_dim is not None)
+        # (the per-head norm is told the key's own size and takes its mean over that)
+        may_pad = rot is None or rot.rotary_dim is not None
         if self.kd % 2 and not may_pad:
             raise ConfigError(f"head_dim {head_dim} must be even where heads rotate or are normed")
         hd = max(self.kd, self.vd)
@@ -98,7 +111,7 @@ class PagedAttention(Mixer):
         self.hd = -(-hd // step) * step
         if self.hd != self.kd and not may_pad:
             raise ConfigError(f"a value size {self.vd} other than the key size {self.kd} cannot be combined "
-                              f"with a rotation or a per-head norm of q and k")
+                              f"with a rotation of the whole head")
         # only the attention kernels that these sizes can reach are compiled for the model
         libs = ["gemm_simt", "attention"]
         if ctx.dtype == torch.bfloat16 and self.hd % 16 == 0 and self.hd <= 128 and self.nq // self.nkv <= 16:
@@ -138,6 +151,9 @@ class PagedAttention(Mixer):
             specs["gate_proj"] = ParamSpec((nq, d))
         if self.value_mix:
             specs["value_mix"] = ParamSpec(())          # (the source layer's own is in the file too, and unused)
+        if self.conv_taps is not None:
+            specs.update({"q_conv": ParamSpec((nq * kd, self.conv_taps)), "k_conv": ParamSpec((nkv * kd, self.conv_taps)),
+                          "v_conv": ParamSpec((nkv * vd, self.conv_taps))})
         return specs
 
     def _pad_heads(self, w, heads, size):
@@ -156,6 +172,12 @@ class PagedAttention(Mixer):
             rows += [self._pad_heads(params["k_proj"].to(dt), self.nkv, self.kd),
                      self._pad_heads(params["v_proj"].to(dt), self.nkv, self.vd)]
         self.head_columns = sum(r.shape[0] for r in rows)       # the gates' columns of the product follow the heads'
+        self.conv_w = None
+        if self.conv_taps is not None:
+            # one tap vector per column of the product, in the columns' order (zeros for the padding, which stays zero)
+            self.conv_w = torch.cat([self._pad_heads(params["q_conv"].to(torch.float32), self.nq, self.kd),
+                                     self._pad_heads(params["k_conv"].to(torch.float32), self.nkv, self.kd),
+                                     self._pad_heads(params["v_conv"].to(torch.float32), self.nkv, self.vd)], 0).contiguous()
         self.qkv_bias = self.o_bias = None
         if self.has_bias:
             # added in float32 to the product's columns by the prepare kernel (zeros for the padding), and laid down
@@ -183,21 +205,35 @@ class PagedAttention(Mixer):
         # the output projection's columns, head by head, with zero columns for the padding
         self.wo = self._pad_heads(params["o_proj"].to(dt).t().contiguous(), self.nq, self.vd).t().contiguous()
         if self.qk_norm_gain:
-            self.qk_norm = QkNorm(self.qk_norm_eps, self.qk_norm_before_rotation,
-                                  params["q_norm"].to(torch.float32).contiguous(),
-                                  params["k_norm"].to(torch.float32).contiguous())
+            def gain(name):                                      # (zeros for the padding of a head)
+                g = torch.zeros((self.hd,), dtype=torch.float32, device=params[name].device)
+                g[:self.kd] = params[name].to(torch.float32)
+                return g.contiguous()
+            self.qk_norm = QkNorm(self.qk_norm_eps, self.qk_norm_before_rotation, gain("q_norm"), gain("k_norm"))
 
     def weight_bytes(self):
         return (self.wqkv.numel() + self.wo.numel()) * self.wqkv.element_size()
 
     def cache_request(self):
-        return PagedKV(self.window, self.nkv, self.hd), None
+        state = None
+        if self.conv_taps is not None and self.conv_taps > 1:
+            state = FixedState(((self.conv_taps - 1) * (self.nq + 2 * self.nkv) * self.hd,), torch.float32)
+        return PagedKV(self.window, self.nkv, self.hd), state
 
     def forward(self, x, h, batch, cache, accumulate=True):
         M = x.shape[0]
         k = self.k
         qkv = torch.empty((M, self.wqkv.shape[0]), dtype=x.dtype, device=x.device)
-        k.linear(x, self.wqkv, qkv)
+        if self.conv_w is None:
+            k.linear(x, self.wqkv, qkv)
+        else:
+            # the projection's float32 sums pass the convolution over time; the gates' columns behind them pass unchanged
+            proj = torch.empty((M, self.wqkv.shape[0]), dtype=torch.float32, device=x.device)
+            k.linear(x, self.wqkv, proj)
+            if self.conv_taps > 1:
+                k.short_conv(proj, self.conv_w, qkv, batch, cache.state, channels=self.head_columns)
+            else:
+                k.short_conv(proj, self.conv_w, qkv, batch, proj, channels=self.head_columns)
         q = torch.empty((M, self.nq * self.hd), dtype=x.dtype, device=x.device)
         extra = {}
         gates = None
@@ -215,6 +251,8 @@ class PagedAttention(Mixer):
             extra["value_mix"] = (src[0], src[1], src[2], self.vd, self.value_lambda)
         if self.qkv_bias is not None:
             extra["bias"] = self.qkv_bias
+        if self.qk_norm is not None and self.hd != self.kd:
+            extra["norm_dim"] = self.kd
         if self.kv_shared:
             if cache.write:
                 raise ConfigError("a layer without keys and values of its own was given a cache to write")
@@ -231,6 +269,8 @@ class PagedAttention(Mixer):
             more["head_slopes"] = self._slopes
         if gates is not None:
             more["head_gates"] = gates
+        if self.score_softcap is not None:
+            more["score_softcap"] = self.score_softcap
         k.paged_attention(q, o, batch, cache, num_heads=self.nq, window=self.window,
                           softmax_scale=self.softmax_scale, cache_settled=True, sink_logit=self.sink_logit, **more)
         if self.output_gate:

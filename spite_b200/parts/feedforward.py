@@ -214,26 +214,48 @@ class MoESoftmaxTopK(FeedForward):
         w_e = s_e / (sum of the chosen s + 1e-20);  h += sum_e w_e * down_e( silu(gate_e x) * (up_e x) )
 
     The weight multiplies the float32 sums of the expert's last product as they are added to the residual
-    stream, so no rounded intermediate carries it."""
+    stream, so no rounded intermediate carries it.
+
+    Variants, all parameters: `renormalize` False leaves the chosen shares as they are (w_e = s_e); `choice_bias` adds a
+    learned constant per expert (`choice_bias` [experts]) to the shares for the choice alone, the weights stay the
+    shares; `identity_experts` n: the router has n outputs more than there are experts, and a token that draws one of
+    those gets its own input back, times the weight (such an expert has no tensors)."""
     graph_safe = True
+    can_store = True
     kernel_libraries = ("gemm_simt", "moe")
 
-    def __init__(self, ctx, hidden_size: int, num_experts: int, top_k: int, expert_size: int):
+    def __init__(self, ctx, hidden_size: int, num_experts: int, top_k: int, expert_size: int, renormalize: bool = True,
+                 choice_bias: bool = False, identity_experts: int = 0):
         super().__init__(ctx)
-        if not 1 <= top_k <= num_experts:
-            raise ConfigError(f"top_k {top_k} must lie in 1..{num_experts}")
+        self.identity = int(identity_experts)
+        if self.identity < 0 or num_experts < 0 or num_experts + self.identity < 1:
+            raise ConfigError("a mixture needs at least one expert")
+        if not 1 <= top_k <= num_experts + self.identity:
+            raise ConfigError(f"top_k {top_k} must lie in 1..{num_experts + self.identity}")
+        self.renormalize, self.has_choice_bias = bool(renormalize), bool(choice_bias)
+        if self.renormalize and (self.has_choice_bias or self.identity):
+            raise ConfigError("a choice bias and identity experts go with weights that are not renormalised")
         self.d, self.E, self.top_k, self.f = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
-        self.router = self.w_gate_up = self.w_down = None
+        self.router = self.w_gate_up = self.w_down = self.choice_bias = None
         self.keep_router_logits = False      # `last_routing.logits` [tokens, experts] stays readable after a forward
 
     def param_specs(self):
         d, E, f = self.d, self.E, self.f
-        return {"router": ParamSpec((E, d)), "experts_gate": ParamSpec((E, f, d)), "experts_up": ParamSpec((E, f, d)),
-                "experts_down": ParamSpec((E, d, f))}
+        specs = {"router": ParamSpec((E + self.identity, d)), "experts_gate": ParamSpec((E, f, d)),
+                 "experts_up": ParamSpec((E, f, d)), "experts_down": ParamSpec((E, d, f))}
+        if self.has_choice_bias:
+            specs["choice_bias"] = ParamSpec((E + self.identity,))
+        return specs
 
     def bind(self, params):
         dt = self.ctx.dtype
         self.router = params["router"].to(torch.float32).contiguous()        # float32 sums of float32 weights
+        if self.renormalize:
+            self.choice_bias = None
+        elif self.has_choice_bias:
+            self.choice_bias = params["choice_bias"].to(torch.float32).contiguous()
+        else:
+            self.choice_bias = torch.zeros((self.E + self.identity,), dtype=torch.float32, device=self.router.device)
         self.w_gate_up = torch.cat([params["experts_gate"].to(dt), params["experts_up"].to(dt)], 1).contiguous()
         self.w_down = params["experts_down"].to(dt).contiguous()
 
@@ -245,13 +267,27 @@ class MoESoftmaxTopK(FeedForward):
         per = 3 * self.f * self.d * self.w_down.element_size()
         return int(per * n_distinct_experts) + self.router.numel() * 4
 
-    def forward(self, x, h, batch):
+    def forward(self, x, h, batch, accumulate=True):
         k = self.k
         M = x.shape[0]
-        routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits, scoring="softmax_renorm")
+        if self.renormalize:
+            routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits, scoring="softmax_renorm")
+        else:
+            routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits, scoring="softmax_biased",
+                                  choice_bias=self.choice_bias)
         self.last_routing = routing
+        if self.identity:
+            # the tokens that drew an identity expert get their input back, times the weight; without `accumulate` this
+            # also starts every row of the sum that the experts then add to
+            k.moe_identity(x, routing, self.E, h, accumulate=accumulate)
+        elif not accumulate:
+            h.zero_()
+        if not self.E:
+            return
         for slot in range(self.top_k):
             a = torch.empty((M, self.f), dtype=x.dtype, device=x.device)
-            k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot], None, a)
-            k.grouped_linear_accumulate(a, self.w_down, routing.sorted_rows[slot], routing.offsets[slot], h,
+            # (the experts' ranges of the sorted order come first; the places behind them belong to identity experts)
+            offsets = routing.offsets[slot][:self.E + 1]
+            k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], offsets, None, a)
+            k.grouped_linear_accumulate(a, self.w_down, routing.sorted_rows[slot], offsets, h,
                                         row_scale=routing.sorted_weights[slot])

@@ -14,8 +14,9 @@ step's tokens only:
 
 so the attention kernels see `num_heads` query heads on one key head whose rows are [c ; k_r], and the products
 with W_uk,h^T before and W_uv,h after them are products per head over the (token, head) rows.  The score's scale
-is a parameter; every earlier position is visible.  An optional gate multiplies head h's output by
-sigmoid(w_h . x); it is applied to the attention's result before W_uv,h, which is the same product.
+is a parameter, and so is the window (every earlier position, the query's chunk, or the last W positions).  An
+optional gate multiplies head h's output by sigmoid(w_h . x); it is applied to the attention's result before W_uv,h,
+which is the same product.  An optional learned sink per head adds exp(sink_h) to the softmax's sum.
 
 Steps of `forward`: one product for W_dq, W_dkv and the gates' rows (float32 sums kept); `latent_prepare` (both
 norms in float32, the rotation of k_r, the cache row, the gates); W_uq; `latent_queries` (rotation of q_r into
@@ -34,13 +35,16 @@ from .base import Mixer, ParamSpec, build_part, register_mixer
 @register_mixer("latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
+    can_store = True
 
     def __init__(self, ctx, hidden_size: int, num_heads: int, head_dim: int, rotary_dim: int, value_dim: int,
                  q_rank: int, kv_rank: int, softmax_scale: float, norm_eps: float, position: PartSpec,
-                 head_gate: bool = False):
+                 head_gate: bool = False, window=("full", 0), head_sinks: bool = False):
         """`head_dim` is the unrotated part of a query/key head, `rotary_dim` the rotated part, `value_dim` a value
         head; `q_rank` and `kv_rank` are the sizes of the two latents, both RMS-normed (gains `q_latent_norm`,
-        `kv_latent_norm`, eps `norm_eps`).  `position` must rotate exactly `rotary_dim` elements."""
+        `kv_latent_norm`, eps `norm_eps`).  `position` must rotate exactly `rotary_dim` elements (either pairing).
+        `window`: which earlier positions a query sees.  `head_sinks`: a learned score per head (`sinks` [heads]) whose
+        exponential joins the softmax's denominator and nothing else."""
         super().__init__(ctx)
         self.d, self.nq = int(hidden_size), int(num_heads)
         self.dn, self.dr, self.dv = int(head_dim), int(rotary_dim), int(value_dim)
@@ -49,10 +53,12 @@ class LatentAttention(Mixer):
             raise ConfigError("latent attention needs positive sizes and an even rotary_dim")
         self.softmax_scale, self.eps = float(softmax_scale), float(norm_eps)
         self.head_gate = bool(head_gate)
+        self.has_head_sinks = bool(head_sinks)
+        self.window = window if isinstance(window, Window) else Window(window[0], int(window[1]))
         self.position = build_part("position", position, ctx)
         rot = self.position.rotation()
-        if rot is None or rot.pairing != "neighbours" or (rot.rotary_dim or self.dr) != self.dr:
-            raise ConfigError(f"latent attention needs a rotation of neighbouring pairs over its {self.dr} rotating elements")
+        if rot is None or (rot.rotary_dim or self.dr) != self.dr or 2 * rot.inv_freq.numel() != self.dr:
+            raise ConfigError(f"latent attention needs a rotation over exactly its {self.dr} rotating elements")
         # a cache row is [latent ; shared key part], in bfloat16 rounded up to the tensor-core kernels' step of 16
         # (the padding is zeros on both sides of every score); the general kernels take even sizes
         row = self.rkv + self.dr
@@ -67,7 +73,7 @@ class LatentAttention(Mixer):
                 libs += ["attention_tc", "attention_decode"]
         self.kernel_libraries = tuple(libs)
         self.down_cols = self.rq + self.rkv + self.dr + (self.nq if self.head_gate else 0)
-        self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.wo = self.q_gain = self.kv_gain = None
+        self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.wo = self.q_gain = self.kv_gain = self.sinks = None
 
     def param_specs(self):
         d, nq = self.d, self.nq
@@ -78,6 +84,8 @@ class LatentAttention(Mixer):
                  "o_proj": ParamSpec((d, nq * self.dv))}
         if self.head_gate:
             specs["gate_proj"] = ParamSpec((nq, d))
+        if self.has_head_sinks:
+            specs["sinks"] = ParamSpec((nq,))
         return specs
 
     def bind(self, params):
@@ -96,15 +104,17 @@ class LatentAttention(Mixer):
         self.wo = params["o_proj"].to(dt).contiguous()
         self.q_gain = params["q_latent_norm"].to(torch.float32).contiguous()
         self.kv_gain = params["kv_latent_norm"].to(torch.float32).contiguous()
+        if self.has_head_sinks:
+            self.sinks = params["sinks"].to(torch.float32).contiguous()
 
     def weight_bytes(self):
         n = sum(t.numel() for t in (self.w_down, self.w_uq, self.w_uk_t, self.w_uv, self.wo))
         return n * self.wo.element_size() + (self.q_gain.numel() + self.kv_gain.numel()) * 4
 
     def cache_request(self):
-        return PagedKV(Window("full", 0), 1, self.row, planes=1), None
+        return PagedKV(self.window, 1, self.row, planes=1), None
 
-    def forward(self, x, h, batch, cache):
+    def forward(self, x, h, batch, cache, accumulate=True):
         M, k, dev = x.shape[0], self.k, x.device
         nq, row = self.nq, self.row
         down = torch.empty((M, self.w_down.shape[0]), dtype=torch.float32, device=dev)
@@ -127,8 +137,10 @@ class LatentAttention(Mixer):
         k.grouped_linear_rows(qn, self.w_uk_t, rows, offsets, qa.view(M * nq, row), a_sorted=True)
         ol = torch.empty((nq * M, row), dtype=x.dtype, device=dev)           # head by head, as the next product reads it
         more = {"head_gates": gates} if gates is not None else {}
-        k.paged_attention(qa, ol, batch, cache, num_heads=nq, window=Window("full", 0),
+        if self.sinks is not None:
+            more["head_sinks"] = self.sinks
+        k.paged_attention(qa, ol, batch, cache, num_heads=nq, window=self.window,
                           softmax_scale=self.softmax_scale, cache_settled=True, out_by_head=True, **more)
         o = torch.empty((M, nq * self.dv), dtype=x.dtype, device=dev)
         k.grouped_linear_rows(ol, self.w_uv, rows, offsets, o.view(M * nq, self.dv), a_sorted=True)
-        k.linear(o, self.wo, h, accumulate=True)
+        k.linear(o, self.wo, h, accumulate=accumulate)

@@ -54,8 +54,66 @@ class TorchReferenceKernels(KernelSet):
         v = y.to(self.acc)
         v = v * (1.0 / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)) * gain.to(self.acc)
         h.add_((mult * v).to(h.dtype))
-        if next_out is not None:
+        if next_out is not None and next_gain is None:
+            next_out.copy_(h.to(next_out.dtype))
+        elif next_out is not None:
             self.rms_norm(h, next_gain, eps, next_out)
+
+    def cast_rows(self, h, out):
+        out.copy_(h.to(out.dtype))
+
+    def short_conv(self, x, w, out, batch, state, *, channels, activation=None, state_offset=0):
+        taps = w.shape[1]
+        cu = batch.cu_seqlens.tolist()
+        slots = batch.slots.tolist()
+        xv, wv = x.to(self.acc), w.to(self.acc)
+        out[:, channels:] = x[:, channels:out.shape[1]].to(out.dtype)
+        for s in range(len(cu) - 1):
+            if s > 0 and slots[s] == slots[0]:                  # a padding copy of the first row comes out as that row does
+                n = min(cu[s + 1] - cu[s], cu[1] - cu[0])
+                out[cu[s]:cu[s] + n] = out[cu[0]:cu[0] + n]
+                continue
+            st = state[slots[s]].reshape(-1)[state_offset:state_offset + (taps - 1) * channels].view(taps - 1, channels)
+            hist = torch.cat([st.to(self.acc), xv[cu[s]:cu[s + 1], :channels]], 0)       # rows -(taps-1) .. n-1
+            for i in range(cu[s + 1] - cu[s]):
+                y = torch.zeros(channels, dtype=self.acc)
+                for j in range(taps):
+                    y = y + wv[:, j] * hist[i + j]
+                if activation == "silu":
+                    y = y * torch.sigmoid(y)
+                out[cu[s] + i, :channels] = y.to(out.dtype)
+            if taps > 1:
+                st.copy_(hist[hist.shape[0] - (taps - 1):].to(st.dtype))
+
+    def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
+                   unit_eps=1e-6, state_offset=0):
+        qc, kc, vc, bc, ac = columns
+        xv = x.to(self.acc)
+        cu = batch.cu_seqlens.tolist()
+        slots = batch.slots.tolist()
+        for s in range(len(cu) - 1):
+            if s > 0 and slots[s] == slots[0]:                  # a padding copy of the first row
+                out[cu[s]:cu[s + 1]] = 0
+                continue
+            flat = state[slots[s]].reshape(-1)
+            for a in range(heads):
+                g = a // (heads // kv_heads)
+                st = flat[state_offset + a * dim * vdim:state_offset + (a + 1) * dim * vdim]
+                S = st.to(self.acc).reshape(dim, vdim).clone()
+                for t in range(cu[s], cu[s + 1]):
+                    q = xv[t, qc + g * dim:qc + (g + 1) * dim]
+                    k = xv[t, kc + g * dim:kc + (g + 1) * dim]
+                    v = xv[t, vc + a * vdim:vc + (a + 1) * vdim]
+                    q = q / torch.sqrt((q * q).sum() + unit_eps) * q_scale
+                    k = k / torch.sqrt((k * k).sum() + unit_eps)
+                    beta = torch.sigmoid(xv[t, bc + a])
+                    decay = torch.exp(-torch.exp(a_log[a].to(self.acc)) *
+                                      torch.nn.functional.softplus(xv[t, ac + a] + dt_bias[a].to(self.acc)))
+                    S = decay * S
+                    u = beta * (v - S.T @ k)
+                    S = S + torch.outer(k, u)
+                    out[t, a * vdim:(a + 1) * vdim] = (S.T @ q).to(out.dtype)
+                st.copy_(S.reshape(-1).to(st.dtype))
 
     def fill_rows(self, out, vec, *, accumulate=False):
         if accumulate:
@@ -63,7 +121,7 @@ class TorchReferenceKernels(KernelSet):
         else:
             out.copy_(vec[None, :].to(out.dtype).expand_as(out))
 
-    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None):
+    def head_norm_gate(self, x, out, *, heads, size, gates=None, gate_column=0, gain=None, eps=None, gate_activation="sigmoid"):
         M = x.shape[0]
         v = x.to(self.acc).reshape(M, heads, size)
         if eps is not None:
@@ -72,7 +130,8 @@ class TorchReferenceKernels(KernelSet):
         if gain is not None:
             v = v * gain.to(self.acc)
         if gates is not None:
-            v = v * torch.sigmoid(gates[:, gate_column:gate_column + heads * size].to(self.acc))
+            z = gates[:, gate_column:gate_column + heads * size].to(self.acc)
+            v = v * (torch.sigmoid(z) * z if gate_activation == "silu" else torch.sigmoid(z))
         out.copy_(v.to(out.dtype))
 
     # ---- recurrent mixers
@@ -194,7 +253,7 @@ class TorchReferenceKernels(KernelSet):
 
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature,
-                   value_mix=None, gates_out=None, bias=None, q_only=False):
+                   value_mix=None, gates_out=None, bias=None, q_only=False, norm_dim=None):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -219,7 +278,7 @@ class TorchReferenceKernels(KernelSet):
                 v[:, g, :vd] = (1.0 - lam) * v[:, g, :vd] + lam * o
 
         def norm(t, gain):
-            t = t * (1.0 / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + qk_norm.eps))
+            t = t * (1.0 / torch.sqrt(t.pow(2).sum(-1, keepdim=True) / (norm_dim or hd) + qk_norm.eps))
             return t if gain is None else t * gain.to(t.device, self.acc)
 
         if qk_norm is not None and qk_norm.before_rotation:
@@ -260,12 +319,18 @@ class TorchReferenceKernels(KernelSet):
                 kv[1, page, :, p % P, :] = v[t].to(kv.dtype)
 
     def _rotate_pairs(self, t, pos, rotation):
-        """t [M, ..., rot]: neighbouring pairs turn by pos * inv_freq, times the amplitude."""
+        """t [M, ..., rot]: neighbouring pairs (or element i with i + rot/2) turn by pos * inv_freq, times the amplitude."""
         ang = (pos.to(torch.float32)[:, None] * rotation.inv_freq.to(t.device, torch.float32)[None, :]).to(self.acc)
         shape = [t.shape[0]] + [1] * (t.dim() - 2) + [ang.shape[1]]
         cos, sin = (torch.cos(ang) * rotation.amplitude).view(shape), (torch.sin(ang) * rotation.amplitude).view(shape)
-        a, b = t[..., 0::2], t[..., 1::2]
         o = torch.empty_like(t)
+        if rotation.pairing == "halves":
+            half = t.shape[-1] // 2
+            a, b = t[..., :half], t[..., half:]
+            o[..., :half] = a * cos - b * sin
+            o[..., half:] = a * sin + b * cos
+            return o
+        a, b = t[..., 0::2], t[..., 1::2]
         o[..., 0::2] = a * cos - b * sin
         o[..., 1::2] = a * sin + b * cos
         return o
@@ -313,7 +378,8 @@ class TorchReferenceKernels(KernelSet):
             sorted_out.copy_(q.view(M, num_heads, head_dim + rot)[:, :, :head_dim].transpose(0, 1).reshape(num_heads * M, head_dim))
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False,
-                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False):
+                        sink_logit=None, head_sinks=None, head_slopes=None, head_gates=None, out_by_head=False,
+                        score_softcap=None):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -333,6 +399,8 @@ class TorchReferenceKernels(KernelSet):
             V = kv[kv.shape[0] - 1, pages, :, js % P, :].to(self.acc)     # (one plane: the key rows are the values)
             for h in range(nq):
                 s = (K[:, h // group, :] @ qf[t, h]) * softmax_scale
+                if score_softcap is not None:
+                    s = score_softcap * torch.tanh(s / score_softcap)
                 if head_slopes is not None:
                     s = s - float(head_slopes[h]) * (p - js).to(self.acc)
                 sink = sink_logit if head_sinks is None else float(head_sinks[h])
@@ -349,12 +417,25 @@ class TorchReferenceKernels(KernelSet):
                     out[t, h * hd:(h + 1) * hd] = o.to(out.dtype)
 
     # ---- mixture of experts
-    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid") -> Routing:
+    def moe_identity(self, x, routing, first_identity, out, *, accumulate=True):
+        w = (routing.weights * (routing.expert_ids >= first_identity)).sum(0).to(self.acc)      # [M]
+        y = w[:, None] * x.to(self.acc)
+        if accumulate:
+            out.add_(y.to(out.dtype))
+        else:
+            out.copy_(y.to(out.dtype))
+
+    def moe_route(self, x, w_router, top_k, want_logits=False, scoring="sigmoid", choice_bias=None) -> Routing:
         logits = (x.to(torch.float32) @ w_router.to(torch.float32).T)
         order = torch.sort(logits, dim=-1, descending=True, stable=True)
+        if scoring == "softmax_biased":
+            share = torch.softmax(logits, -1)
+            order = torch.sort(share + choice_bias.to(torch.float32)[None, :], dim=-1, descending=True, stable=True)
         ids = order.indices[:, :top_k].T.contiguous().to(torch.int32)        # [k, M]
         if scoring == "sigmoid":
             w = (1.0 / (1.0 + torch.exp(-order.values[:, :top_k]))).T.contiguous()
+        elif scoring == "softmax_biased":
+            w = share.gather(1, order.indices[:, :top_k]).T.contiguous()
         else:
             assert scoring == "softmax_renorm"
             share = torch.softmax(logits, -1).gather(1, order.indices[:, :top_k])

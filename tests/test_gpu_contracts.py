@@ -183,9 +183,9 @@ def test_router_entry_point(libs):
                  offs=ptr(offs), rows=ptr(rows))
         a.update(kw)
         return lib.spite_moe_route(1, a["x"], a["w"], a["M"], a["d"], a["E"], a["k"], a["ids"], a["wts"],
-                                   a["logits"], a["offs"], a["rows"], a.get("scoring", 0), None, None)
+                                   a["logits"], a["offs"], a["rows"], a.get("scoring", 0), None, None, None)
     for kw in (dict(x=None), dict(w=None), dict(ids=None), dict(wts=None), dict(offs=None), dict(rows=None),
-               dict(M=-1), dict(d=0), dict(E=0), dict(k=0), dict(k=E + 1), dict(scoring=2)):
+               dict(M=-1), dict(d=0), dict(E=0), dict(k=0), dict(k=E + 1), dict(scoring=2), dict(scoring=3)):
         assert call(**kw) == BAD_ARG, kw
     assert call(E=5000) == UNSUPPORTED
     assert untouched(ids, rows, wts, logits, offs)
