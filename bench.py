@@ -14,6 +14,7 @@ Two further workloads print a line of the same kind (they are extra modes; the d
                                          # 8,192, then 256 decode steps at batch 1 and at batch 4
     python bench.py --config mibezen     # the Mibezen design beside Llama 4 at equal layer sizes, measured the same way
     python bench.py --config paposun     # the Paposun design beside a dense Llama 4 at equal layer sizes, measured the same way
+    python bench.py --config gapevik     # the Gapevik design beside Llama 4 at equal layer sizes, measured the same way
     python bench.py --config sezazen     # the Sezazen design beside Llama 4 at equal layer sizes (three sizes): prefill
                                          # of 2,048 tokens and decode at batch 1 and 8, each with its roofline fraction
 """
@@ -363,6 +364,33 @@ def paposun_configs(size, runs=8):
     return pap, llama
 
 
+def gapevik_configs(size, runs=8):
+    """A Gapevik model of eight layer runs (attention with a convolution on q, k, v and capped scores; latent attention
+    through a window with sinks; the gated delta rule; the first attention layer's weights again; and so on: three
+    attention runs on one set of weights, three latent layers, two delta layers, experts with two identity experts
+    everywhere) and a Llama 4 model of eight layers with the same width, experts and vocabulary, whose attention has
+    the heads of Gapevik's attention layers.  A latent row is kv_rank + rot_dim = 128 elements; chunk and window are
+    longer than the measured contexts, so every earlier key is read.  A delta layer has width / 128 heads of 128 x 128
+    on half as many q/k heads."""
+    name, d, nq, nkv, kd, vd, E, top, f, fs, fd, V = size
+    att = {"heads": nq, "kv_heads": nkv, "dim": kd, "vdim": kd, "scale": kd ** -0.5, "mask": {"size": 8192}, "softcap": 30.0,
+           "conv": 4, "rot": {"base": 500000.0, "dims": kd // 2}}
+    lat = {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": d // 4, "kv_rank": 96, "scale": 96 ** -0.5,
+           "mask": {"size": 8192}, "rot": {"base": 20000.0, "dims": 32}}
+    dlt = {"heads": d // 128, "kv_heads": d // 256, "dim": 128, "vdim": 128, "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": f}, "router": {"experts": E, "identity": 2, "top": top}}
+    L = lambda t, m, **kw: dict({"type": t, "mixer": m, "mlp": moe}, **kw)
+    gap = {"architecture": "Gapevik", "vocab": V, "width": d, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+           "embedding": {"scale": d ** 0.5},
+           "layers": [L("attention", att), L("latent_attention", lat), L("delta", dlt), L("attention", att, weights_of=0),
+                      L("latent_attention", lat), L("delta", dlt), L("attention", att, weights_of=0), L("latent_attention", lat)]}
+    llama = dict(SCOUT, num_hidden_layers=runs, hidden_size=d, num_attention_heads=nq, num_key_value_heads=nkv,
+                 head_dim=kd, num_local_experts=E, num_experts_per_tok=top, intermediate_size=f,
+                 intermediate_size_mlp=fd, moe_layers=list(range(runs)), vocab_size=V, tie_word_embeddings=True,
+                 max_position_embeddings=8192)
+    return gap, llama
+
+
 def design_work(model, T, contexts):
     """(flops of a prompt of T tokens, bytes a decode step over `contexts` must read), from the parts' own sizes
     as the design states them (no padding): every layer run reads its weights once; experts by the tokens' draw."""
@@ -370,6 +398,7 @@ def design_work(model, T, contexts):
     from spite_b200.parts.feedforward import DenseActivation, MoESigmoidPrescaled, MoESoftmaxTopK
     from spite_b200.parts.latent import LatentAttention
     from spite_b200.parts.mlstm import MatrixLstm
+    from spite_b200.parts.delta import GatedDelta
     es, p = 2, model.plan
     flops, nbytes = 2 * p.hidden_size * p.vocab_size, p.vocab_size * p.hidden_size * es
     for j in model.junctions:
@@ -392,6 +421,12 @@ def design_work(model, T, contexts):
             w = d * (2 * m.H * m.kd + 2 * m.H * m.vd + 2 * m.H) + m.H * m.vd * d
             flops += 2 * T * w + 4 * T * m.H * m.kd * m.vd
             nbytes += w * es + len(contexts) * 2 * m.H * (m.kd * m.vd + m.kd + 1) * 4
+        elif isinstance(m, GatedDelta):
+            # projections (q, k, v, the gate, two numbers a head) and the output; per token and head the matrix's decay
+            # and correction and its read-out, two multiply-adds an element; a decode step reads and writes the matrices
+            w = d * (2 * m.G * m.kd + 2 * m.H * m.vd + 2 * m.H) + m.H * m.vd * d
+            flops += 2 * T * w + 4 * T * m.H * m.kd * m.vd
+            nbytes += w * es + len(contexts) * 2 * m.H * m.kd * m.vd * 4
         else:
             shared = getattr(m, "kv_shared", False)
             w = d * (m.nq * m.kd + (0 if shared else m.nkv * (m.kd + m.vd))) + m.nq * m.vd * d + \
@@ -403,8 +438,8 @@ def design_work(model, T, contexts):
             continue
         if isinstance(f, MoESoftmaxTopK):
             used = torch_unique(f)
-            flops += 2 * T * d * (f.E + 3 * f.top_k * f.f)
-            nbytes += 3 * d * used * f.f * es + f.E * d * 4
+            flops += 2 * T * d * (f.E + f.identity + 3 * f.top_k * f.f)
+            nbytes += 3 * d * used * f.f * es + (f.E + f.identity) * d * 4
         elif isinstance(f, DenseActivation):
             flops += 2 * T * 2 * d * f.f
             nbytes += 2 * d * f.f * es
@@ -422,7 +457,10 @@ def design_work(model, T, contexts):
 def torch_unique(ffn):
     import torch
     r = getattr(ffn, "last_routing", None)
-    return int(torch.unique(r.expert_ids).numel()) if r is not None else ffn.E
+    if r is None:
+        return ffn.E
+    ids = torch.unique(r.expert_ids)
+    return int((ids < ffn.E).sum())                  # (identity experts have no weights to read)
 
 
 def run_sezazen(args):
@@ -431,7 +469,8 @@ def run_sezazen(args):
     tokens (a fraction of the copy bandwidth).  One JSON line; `value` is the design's decode rate at batch 8 at
     the first size."""
     design = args.config
-    configs_of = {"sezazen": design_configs, "mibezen": mibezen_configs, "paposun": paposun_configs}[design]
+    configs_of = {"sezazen": design_configs, "mibezen": mibezen_configs, "paposun": paposun_configs,
+                  "gapevik": gapevik_configs}[design]
     import torch
     from spite_b200.config import config_from_dict
     from spite_b200.engine import Engine, Model, StepEntry
@@ -712,8 +751,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen", "mibezen", "paposun"], default="scout",
-                    help="scout: the benchmark line; maverick, long, sezazen, mibezen, paposun: further workloads, one line each")
+    ap.add_argument("--config", choices=["scout", "maverick", "long", "sezazen", "mibezen", "paposun", "gapevik"], default="scout",
+                    help="scout: the benchmark line; maverick, long, sezazen, mibezen, paposun, gapevik: further workloads, one line each")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -723,8 +762,8 @@ def main(argv=None):
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
     ap.add_argument("--verbose", action="store_true", help="print the single prefill timings to standard error")
     ap.add_argument("--size", default=None, help="--config sezazen: only this set of layer sizes (small, medium, ...)")
-    ap.add_argument("--design", choices=["both", "sezazen", "mibezen", "paposun", "llama4"], default="both",
-                    help="--config sezazen / mibezen / paposun: only this design")
+    ap.add_argument("--design", choices=["both", "sezazen", "mibezen", "paposun", "gapevik", "llama4"], default="both",
+                    help="--config sezazen / mibezen / paposun / gapevik: only this design")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)
@@ -737,7 +776,7 @@ def main(argv=None):
     if args.config == "long":
         run_long(args)
         return 0
-    if args.config in ("sezazen", "mibezen", "paposun"):
+    if args.config in ("sezazen", "mibezen", "paposun", "gapevik"):
         run_sezazen(args)
         return 0
     if args.warmup < 3:

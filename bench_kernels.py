@@ -13,6 +13,7 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py --only gated_less    # experts without a gate (squared ReLU), the junction of a loop,
                                                  # the embedding with learned positions
     python bench_kernels.py --only recurrent     # the matrix memory's scan in prompts and decode steps, the heads' norm
+    python bench_kernels.py --only delta         # the gated delta rule's scan in prompts and decode steps, the short convolution
                                                  # and gate, the norm behind a sublayer
 
 Families: gemm_decode (weight streaming, mma.sync), gemm_prefill (tcgen05/TMA),
@@ -348,6 +349,54 @@ def main(argv=None):
                 return lambda: ks.rms_norm_residual(y, g1, 1e-5, 0.5, h, next_gain=g2, next_out=x)
             nbytes = M * dm * (4 + 4 + 4 + 2)
             report("recurrent", f"rms_norm_residual with the next norm M={M} d={dm}", timed_rotating(make_join, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+
+    # ---- the gated delta rule's scan (heads of 128 x 128 on half as many q/k heads, float32), the convolution over time in
+    # front of it and the cast that a sublayer without a norm in front reads
+    if want("delta"):
+        dm = 2048 if args.small else 4096
+        H, G, kd, vd = dm // 128, dm // 256, 128, 128
+        ch = 2 * G * kd + H * vd
+        cols = (0, G * kd, 2 * G * kd, ch + H * vd, ch + H * vd + H)
+        width = -(-(cols[4] + H) // 8) * 8
+        fma_peak = 148 * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6
+        zero = torch.zeros(H, device=dev)
+        for n_seg, n_tok in ((1, 2048), (8, 2048), (1, 1), (8, 1), (64, 1)):
+            M = n_seg * n_tok
+            segs = [Segment(i, i, 0, n_tok, i * n_tok, True) for i in range(n_seg)]
+            batch = build_step_batch(segs, [[0] * n_tok] * n_seg, [[]] * n_seg, [[[0]] * n_seg], dev)
+            def make_scan(M=M, batch=batch, n_seg=n_seg, split=None):
+                x = torch.randn((M, width), device=dev)
+                out = torch.empty((M, H * vd), device=dev)
+                state = torch.zeros((n_seg, H * kd * vd), device=dev)
+                return lambda: ks.delta_scan(x, out, batch, state, heads=H, kv_heads=G, dim=kd, vdim=vd, columns=cols, a_log=zero - 2.0,
+                                             dt_bias=zero, q_scale=kd ** -0.5, split_rows=split)
+            nbytes = n_seg * H * kd * vd * 4 * 2 + M * (2 * G * kd + 2 * H * vd + 2 * H) * 4
+            flops = 4 * M * H * kd * vd
+            name = f"delta_scan {n_seg} x {n_tok} tokens, {H} heads of {kd} x {vd}"
+            if n_tok > 1:
+                for split in (False, True):
+                    full = name + (", rows split further" if split else ", eight columns a warp")
+                    if args.case and args.case not in full:
+                        continue
+                    ms = timed(make_scan(split=split))()
+                    print(json.dumps({"family": "delta", "case": full, "us": round(ms * 1e3, 2), "TFLOPs_fp32": round(flops / ms / 1e9, 2),
+                                      "fp32_fma_frac": round(flops / (ms * 1e-3) / fma_peak, 3), "GBps": round(nbytes / ms / 1e6, 1),
+                                      "peaks": src}), flush=True)
+            else:
+                report("delta", name, timed_rotating(make_scan, nbytes), nbytes=nbytes)
+            def make_conv(M=M, batch=batch, n_seg=n_seg):
+                x, w = torch.randn((M, width), device=dev), torch.randn((ch, 4), device=dev)
+                out = torch.empty((M, width), device=dev)
+                state = torch.zeros((n_seg, 3 * ch), device=dev)
+                return lambda: ks.short_conv(x, w, out, batch, state, channels=ch, activation="silu")
+            nbytes = M * width * 8 + n_seg * 3 * ch * 8
+            report("delta", f"short_conv {n_seg} x {n_tok} tokens, {ch} channels of 4 taps", timed_rotating(make_conv, max(nbytes, 64 << 20) if n_tok == 1 else nbytes), nbytes=nbytes)
+        for M in (8, 2048):
+            def make_cast(M=M):
+                h, x = torch.randn((M, dm), device=dev), torch.empty((M, dm), dtype=bf, device=dev)
+                return lambda: ks.cast_rows(h, x)
+            nbytes = M * dm * 6
+            report("delta", f"cast_rows M={M} d={dm}", timed_rotating(make_cast, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
 
     # ---- the small kernels of a decode step
     if want("small"):

@@ -141,13 +141,14 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
             float mx = -INFINITY, z = 0.f;
             for (int e = 0; e < n_experts; ++e) mx = fmaxf(mx, l[e]);
             for (int e = 0; e < n_experts; ++e) z += expf(l[e] - mx);
+            const float inv_z = 1.0f / z;                    // (one rounding for every share of the token, choice and weight alike)
             float pv = INFINITY, bv = 0.f;
             int pe = -1, be = 0;
             for (int s = 0; s <= slot; ++s) {
                 bv = -INFINITY;
                 be = -1;
                 for (int e = 0; e < n_experts; ++e) {
-                    const float v = expf(l[e] - mx) / z + choice_bias[e];
+                    const float v = expf(l[e] - mx) * inv_z + choice_bias[e];
                     const bool after_prev = v < pv || (v == pv && e > pe);
                     if (after_prev && (be < 0 || v > bv)) { bv = v; be = e; }
                 }
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __re
                 pe = be;
             }
             ids[t] = be;
-            weights[(size_t)slot * n_tokens + t] = expf(l[be] - mx) / z;
+            weights[(size_t)slot * n_tokens + t] = expf(l[be] - mx) * inv_z;
             atomicAdd(&counts[be + 1], 1);
             continue;
         }

@@ -86,7 +86,8 @@ class KernelSet:
         [channels, taps]; rows before a segment's first token come from the request's slot, state[slot, state_offset :
         state_offset + (taps - 1) * channels] (float32 [taps - 1, channels], oldest first; zeros at the start of a
         sequence), which then receives the sequence's last taps - 1 rows of x.  The c = out.shape[1] - channels columns behind
-        the channels are passed on unchanged.  out [M, channels + c] is T or float32; `activation` None or "silu"."""
+        the channels are passed on unchanged.  out [M, channels + c] is T or float32; `activation` None or "silu".
+        With one tap nothing is carried and `state` may be None."""
         raise NotImplementedError
 
     def fill_rows(self, out, vec, *, accumulate=False):
@@ -217,7 +218,7 @@ class KernelSet:
         return dim * vdim + -(-vdim // 32) * (-(-(dim + 1) // 4) * 4)
 
     def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
-                   unit_eps=1e-6, state_offset=0):
+                   unit_eps=1e-6, state_offset=0, split_rows=None):
         """The gated delta rule, token by token, for every segment of the step from the matrix its request's slot holds
         (zeros: the start of a sequence); the slot receives the matrix after the segment's last token.  x float32 [M, *]
         holds, from the columns `columns` = (q, k, v, b, a) on, q and k [kv_heads * dim], v [heads * vdim] and two
@@ -225,7 +226,8 @@ class KernelSet:
         state[slot, state_offset + h * dim * vdim].  Head h reads q/k head h // (heads / kv_heads).
         k <- k / sqrt(|k|^2 + unit_eps), q <- q / sqrt(|q|^2 + unit_eps) * q_scale, beta = sigmoid(b),
         g = exp(-exp(a_log[h]) * softplus(a + dt_bias[h])); S <- g S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.
-        All float32."""
+        All float32.  `split_rows`: more lanes share a value column's key rows (the same sums in another order; for steps
+        with long segments); None leaves the choice to the kernel set."""
         raise NotImplementedError
 
     # ---- mixture of experts

@@ -90,7 +90,7 @@ class DeltaParams(C.Structure):
                 ("a_log", C.c_void_p), ("dt_bias", C.c_void_p), ("out", C.c_void_p), ("state", C.c_void_p),
                 ("slot_stride", C.c_longlong), ("cu_seqlens", C.c_void_p), ("slots", C.c_void_p),
                 ("n_segments", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
-                ("q_scale", C.c_float), ("unit_eps", C.c_float)]
+                ("q_scale", C.c_float), ("unit_eps", C.c_float), ("gates", C.c_void_p), ("n_tokens", C.c_int)]
 
 
 class MlstmParams(C.Structure):
@@ -407,6 +407,8 @@ class CudaKernels(KernelSet):
 
     def short_conv(self, x, w, out, batch, state, *, channels, activation=None, state_offset=0):
         self._t(x, torch.float32, "x"); self._t(w, torch.float32, "w"); self._t(out, None, "out")
+        if state is None and w.shape[1] == 1:
+            state = x[:1]                                       # one tap: nothing is carried, and the kernel touches no slot
         self._t(state, torch.float32, "state")
         if out.dtype not in (self.dtype, torch.float32):
             raise KernelError(f"short_conv: out must be {self.dtype} or float32")
@@ -999,7 +1001,7 @@ class CudaKernels(KernelSet):
         _check(st, "mlstm_scan")
 
     def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
-                   unit_eps=1e-6, state_offset=0):
+                   unit_eps=1e-6, state_offset=0, split_rows=None):
         self._t(x, torch.float32, "x"); self._t(out, torch.float32, "out"); self._t(state, torch.float32, "state")
         self._t(a_log, torch.float32, "a_log"); self._t(dt_bias, torch.float32, "dt_bias")
         M = x.shape[0]
@@ -1010,14 +1012,23 @@ class CudaKernels(KernelSet):
             raise KernelError("delta_scan: shapes do not fit")
         if max(q_col + kv_heads * dim, k_col + kv_heads * dim, v_col + heads * vdim, b_col + heads, a_col + heads) > x.shape[1]:
             raise KernelError("delta_scan: the columns lie outside the rows of x")
+        # what a token brings besides q, k, v (unit-vector factors, beta, decay): filled by the first of the two kernels
+        gates = torch.empty((M, 2 * kv_heads + 2 * heads), dtype=torch.float32, device=x.device)
         p = DeltaParams(x=x.data_ptr(), stride=x.shape[1], q_col=q_col, k_col=k_col, v_col=v_col, b_col=b_col, a_col=a_col,
                         a_log=a_log.data_ptr(), dt_bias=dt_bias.data_ptr(), out=out.data_ptr(),
                         state=state.data_ptr() + 4 * int(state_offset), slot_stride=slot_stride,
                         cu_seqlens=batch.cu_seqlens.data_ptr(), slots=batch.slots.data_ptr(),
                         n_segments=batch.cu_seqlens.numel() - 1, heads=int(heads), kv_heads=int(kv_heads), dim=int(dim),
-                        vdim=int(vdim), q_scale=float(q_scale), unit_eps=float(unit_eps))
-        st = self._lib("delta").spite_delta_scan(C.byref(p), self._stream())
-        self._count("delta", 1)
+                        vdim=int(vdim), q_scale=float(q_scale), unit_eps=float(unit_eps), gates=gates.data_ptr(), n_tokens=M)
+        if split_rows is None:
+            # A warp on eight value columns (whole sectors of the state per row) serves every step.  More lanes a column
+            # and fewer columns a block was measured and is no faster: the walk's time is the length of its chain per token
+            # (a barrier, the sums, the shuffles), not the multiply-adds (2,048 tokens of 16 heads of 128 x 128: 1.73 ms
+            # against 2.05 ms; eight such prompts 3.48 against 3.98 ms).  One form for every step also keeps the float32
+            # set's results independent of how a prompt was cut, to the last bit.
+            split_rows = False
+        st = self._lib("delta").spite_delta_scan(C.byref(p), C.c_int(int(bool(split_rows))), self._stream())
+        self._count("delta", 2)
         _check(st, "delta_scan")
 
     # ------------------------------------------------------------------ mixture of experts

@@ -230,10 +230,7 @@ class PagedAttention(Mixer):
             # the projection's float32 sums pass the convolution over time; the gates' columns behind them pass unchanged
             proj = torch.empty((M, self.wqkv.shape[0]), dtype=torch.float32, device=x.device)
             k.linear(x, self.wqkv, proj)
-            if self.conv_taps > 1:
-                k.short_conv(proj, self.conv_w, qkv, batch, cache.state, channels=self.head_columns)
-            else:
-                k.short_conv(proj, self.conv_w, qkv, batch, proj, channels=self.head_columns)
+            k.short_conv(proj, self.conv_w, qkv, batch, cache.state, channels=self.head_columns)
         q = torch.empty((M, self.nq * self.hd), dtype=x.dtype, device=x.device)
         extra = {}
         gates = None

@@ -44,6 +44,14 @@ def load_folder(folder):
     return cfg, read_safetensors(f"{folder}/model.safetensors")
 
 
+_round = None      # set by `forward(round_inputs=...)`: what an engine that keeps activations in 16 bits does to them
+
+
+def _in(x):
+    """An input of a matrix product (or an attention's q, k, v), rounded the way `forward` was told to."""
+    return x if _round is None else _round(x)
+
+
 def rms_norm(x, w, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
@@ -92,73 +100,82 @@ def rotate_halves(x, dims, base, positions):
     return out
 
 
-def chunk_visible(i, j, size):
-    return j <= i and i // size == j // size
+def chunk_visible(T, size):
+    """[T, T] bool: query i sees key j <= i of its own chunk, chunks counted from position 0."""
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    return (j <= i) & (torch.div(i, size, rounding_mode="floor") == torch.div(j, size, rounding_mode="floor"))
 
 
-def window_visible(i, j, size):
-    return 0 <= i - j < size
+def window_visible(T, size):
+    """[T, T] bool: query i sees itself and the size - 1 keys before it."""
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    return (i - j >= 0) & (i - j < size)
 
 
 def attention(h, w, mx, eps):
     T = h.shape[0]
     H, G, dim, vdim = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
     pos = torch.arange(T)
-    q = short_conv(h @ w["q"].T, w["q.conv"]).view(T, H, dim)
-    k = short_conv(h @ w["k"].T, w["k.conv"]).view(T, G, dim)
-    v = short_conv(h @ w["v"].T, w["v.conv"]).view(T, G, vdim)
+    h = _in(h)
+    conv = (lambda u, name: short_conv(u, w[name])) if mx.get("conv") else (lambda u, name: u)
+    q = conv(h @ w["q"].T, "q.conv").view(T, H, dim)
+    k = conv(h @ w["k"].T, "k.conv").view(T, G, dim)
+    v = conv(h @ w["v"].T, "v.conv").view(T, G, vdim)
     q = rms_norm(q, w["q.norm"], eps)
     k = rms_norm(k, w["k.norm"], eps)
     rot = mx["rot"]
-    q = rotate_neighbours(q, rot["dims"], rot["base"], pos)
-    k = rotate_neighbours(k, rot["dims"], rot["base"], pos)
+    q = _in(rotate_neighbours(q, rot["dims"], rot["base"], pos))
+    k = _in(rotate_neighbours(k, rot["dims"], rot["base"], pos))
+    v = _in(v)
     gate = torch.sigmoid(h @ w["g"].T)                       # [T, H]
-    cap, size = mx["softcap"], mx["mask"]["size"]
+    cap, size = mx.get("softcap"), (mx["mask"]["size"] if mx.get("mask") else T)
     out = torch.zeros(T, H, vdim, dtype=h.dtype)
+    sees = chunk_visible(T, size)
     for hd in range(H):
         g = hd // (H // G)
-        for i in range(T):
-            js = [j for j in range(T) if chunk_visible(i, j, size)]
-            s = torch.stack([(q[i, hd] * k[j, g]).sum() for j in js]) * mx["scale"]
+        s = (q[:, hd] @ k[:, g].T) * mx["scale"]             # [queries, keys]
+        if cap is not None:
             s = cap * torch.tanh(s / cap)
-            p = torch.softmax(s, 0)
-            out[i, hd] = sum(p[n] * v[j, g] for n, j in enumerate(js)) * gate[i, hd]
-    return out.reshape(T, H * vdim) @ w["o"].T
+        p = torch.softmax(s.masked_fill(~sees, -math.inf), -1)
+        out[:, hd] = (p @ v[:, g]) * gate[:, hd:hd + 1]
+    return _in(out.reshape(T, H * vdim)) @ w["o"].T
 
 
 def latent_attention(h, w, mx, eps):
     T = h.shape[0]
     H, dim, rd, vdim, r = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     pos = torch.arange(T)
-    cq = rms_norm(h @ w["dq"].T, w["dq.norm"], eps)
+    h = _in(h)
+    cq = _in(rms_norm(h @ w["dq"].T, w["dq.norm"], eps))
     q = (cq @ w["uq"].T).view(T, H, dim + rd)
     qn, qr = q[..., :dim], q[..., dim:]
     d = h @ w["dkv"].T
-    c = rms_norm(d[:, :r], w["dkv.norm"], eps)
+    c = _in(rms_norm(d[:, :r], w["dkv.norm"], eps))
     kr = d[:, r:].view(T, 1, rd)
     rot = mx["rot"]
     qr = rotate_halves(qr, rot["dims"], rot["base"], pos)
-    kr = rotate_halves(kr, rot["dims"], rot["base"], pos)[:, 0]
+    kr = _in(rotate_halves(kr, rot["dims"], rot["base"], pos)[:, 0])
     kn = (c @ w["uk"].T).view(T, H, dim)
     v = (c @ w["uv"].T).view(T, H, vdim)
     gate = torch.sigmoid(h @ w["g"].T)
-    size = mx["mask"]["size"]
+    size = mx["mask"]["size"] if mx.get("mask") else T
     out = torch.zeros(T, H, vdim, dtype=h.dtype)
+    sees = window_visible(T, size)
     for hd in range(H):
-        for i in range(T):
-            js = [j for j in range(T) if window_visible(i, j, size)]
-            s = torch.stack([(qn[i, hd] * kn[j, hd]).sum() + (qr[i, hd] * kr[j]).sum() for j in js]) * mx["scale"]
-            sink = w["sink"][hd].to(h.dtype)
-            m = torch.maximum(s.max(), sink)
-            e = torch.exp(s - m)
-            p = e / (e.sum() + torch.exp(sink - m))
-            out[i, hd] = sum(p[n] * v[j, hd] for n, j in enumerate(js)) * gate[i, hd]
-    return out.reshape(T, H * vdim) @ w["o"].T
+        s = (qn[:, hd] @ kn[:, hd].T + qr[:, hd] @ kr.T) * mx["scale"]
+        s = s.masked_fill(~sees, -math.inf)
+        sink = w["sink"][hd].to(h.dtype)
+        m = torch.maximum(s.max(-1, keepdim=True).values, sink)
+        e = torch.exp(s - m)
+        p = e / (e.sum(-1, keepdim=True) + torch.exp(sink - m))          # the sink: in the sum, nowhere else
+        out[:, hd] = (p @ v[:, hd]) * gate[:, hd:hd + 1]
+    return _in(out.reshape(T, H * vdim)) @ w["o"].T
 
 
 def delta(h, w, mx, eps):
     T = h.shape[0]
     H, G, dim, vdim = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    h = _in(h)
     q = silu(short_conv(h @ w["q"].T, w["q.conv"])).view(T, G, dim)
     k = silu(short_conv(h @ w["k"].T, w["k.conv"])).view(T, G, dim)
     v = silu(short_conv(h @ w["v"].T, w["v.conv"])).view(T, H, vdim)
@@ -177,12 +194,13 @@ def delta(h, w, mx, eps):
             S = S + torch.outer(k[t, g], u)
             out[t, hd] = S.T @ q[t, g]
     out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + eps) * w["norm"] * z
-    return out.reshape(T, H * vdim) @ w["o"].T
+    return _in(out.reshape(T, H * vdim)) @ w["o"].T
 
 
 def moe(h, w, ff):
     r = ff["router"]
-    E, I, top = r["experts"], r["identity"], r["top"]
+    E, I, top = r["experts"], r.get("identity", 0), r["top"]
+    h = _in(h)
     s = torch.softmax(h @ w["router"].T, -1)                 # [T, E + I]
     choice = s + w["correction"]
     out = torch.zeros_like(h)
@@ -192,7 +210,7 @@ def moe(h, w, ff):
             if e >= E:
                 out[t] += s[t, e] * h[t]
             else:
-                a = silu(h[t] @ w[f"e{e}.gate"].T) * (h[t] @ w[f"e{e}.up"].T)
+                a = _in(silu(h[t] @ w[f"e{e}.gate"].T) * (h[t] @ w[f"e{e}.up"].T))
                 out[t] += s[t, e] * (a @ w[f"e{e}.down"].T)
     return out
 
@@ -204,11 +222,21 @@ def _sub(tensors, prefix, dtype):
     return {k[len(prefix):]: v.to(dtype) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None):
-    """Logits [T, vocab] of one sequence; `taps`, a list, receives the residual stream after every layer."""
+def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None, round_inputs=None):
+    """Logits [T, vocab] of one sequence; `taps`, a list, receives the residual stream after every layer;
+    `round_inputs`, a function, is applied to every input of a matrix product and to attention's q, k and v."""
+    global _round
+    _round = round_inputs
+    try:
+        return _forward(cfg, tensors, tokens, dtype, taps)
+    finally:
+        _round = None
+
+
+def _forward(cfg, tensors, tokens, dtype, taps):
     eps, mu = cfg["norm"]["eps"], cfg["residual_mult"]
     E = tensors["embed"].to(dtype)
-    x = E[torch.tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = E[torch.tensor(tokens, dtype=torch.long)] * cfg.get("embedding", {}).get("scale", 1.0)
     for i, L in enumerate(cfg["layers"]):
         src = L.get("weights_of", i)
         p = f"l{src}."
@@ -219,4 +247,4 @@ def forward(cfg, tensors, tokens, dtype=torch.float32, taps=None):
             x = x + mu * rms_norm(y, tensors[p + "norm2"].to(dtype), eps)
         if taps is not None:
             taps.append(x.clone())
-    return rms_norm(x, tensors["final.norm"].to(dtype), eps) @ E.T
+    return _in(rms_norm(x, tensors["final.norm"].to(dtype), eps)) @ E.T

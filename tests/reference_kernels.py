@@ -73,7 +73,10 @@ class TorchReferenceKernels(KernelSet):
                 n = min(cu[s + 1] - cu[s], cu[1] - cu[0])
                 out[cu[s]:cu[s] + n] = out[cu[0]:cu[0] + n]
                 continue
-            st = state[slots[s]].reshape(-1)[state_offset:state_offset + (taps - 1) * channels].view(taps - 1, channels)
+            if taps > 1:
+                st = state[slots[s]].reshape(-1)[state_offset:state_offset + (taps - 1) * channels].view(taps - 1, channels)
+            else:
+                st = xv.new_zeros((0, channels))
             hist = torch.cat([st.to(self.acc), xv[cu[s]:cu[s + 1], :channels]], 0)       # rows -(taps-1) .. n-1
             for i in range(cu[s + 1] - cu[s]):
                 y = torch.zeros(channels, dtype=self.acc)
@@ -86,7 +89,7 @@ class TorchReferenceKernels(KernelSet):
                 st.copy_(hist[hist.shape[0] - (taps - 1):].to(st.dtype))
 
     def delta_scan(self, x, out, batch, state, *, heads, kv_heads, dim, vdim, columns, a_log, dt_bias, q_scale,
-                   unit_eps=1e-6, state_offset=0):
+                   unit_eps=1e-6, state_offset=0, split_rows=None):
         qc, kc, vc, bc, ac = columns
         xv = x.to(self.acc)
         cu = batch.cu_seqlens.tolist()
