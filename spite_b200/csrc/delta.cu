@@ -84,7 +84,6 @@ template <int RP, int CW>
 __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaParams p) {
     extern __shared__ __align__(16) float ring[];
     pdl_wait();
-    pdl_launch_dependents();
     constexpr int RS = 32 / CW, COLS = 4 * CW, DPAD = RS * RP;
     constexpr int STAGE = 2 * DPAD + ((COLS + 4 + 3) & ~3);    // k [DPAD], q [DPAD], v [COLS], rk, rq, beta, decay
     const int seg = blockIdx.z, head = blockIdx.y;
@@ -185,6 +184,7 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaParams p) {
         const int row = r * RP + i;
         if (row < dim && col_ok) st[(size_t)row * vdim + j] = S[i];
     }
+    pdl_launch_dependents();                                   // (late: the next kernel's blocks would only sit and wait)
 }
 
 template <int RP, int CW>
@@ -192,7 +192,10 @@ static int launch_scan(const DeltaParams& p, cudaStream_t st) {
     constexpr int RS = 32 / CW, COLS = 4 * CW, DPAD = RS * RP;
     constexpr int STAGE = 2 * DPAD + ((COLS + 4 + 3) & ~3);
     dim3 grid((p.vdim + COLS - 1) / COLS, p.heads, p.n_segments);
-    SPITE_LAUNCH((delta_scan_kernel<RP, CW>), grid, 128, (size_t)NBUF * STAGE * sizeof(float), st, p);
+    // Launched in the ordinary way, not as a programmatic dependent: started early, the walk's few blocks take whatever
+    // multiprocessors the kernel before frees first, several to one, and stay there for the whole walk (2,048 tokens
+    // of 16 heads of 128 x 128: 1.40 to 1.78 ms against 1.14 ms).
+    delta_scan_kernel<RP, CW><<<grid, 128, (size_t)NBUF * STAGE * sizeof(float), st>>>(p);
     return spite_launch_status();
 }
 
