@@ -2,9 +2,10 @@
 
 The file lists the layers one by one: `layers[i]` gives the layer's `type` (which mixer it has), the mixer's sizes
 and constants (`mixer`) and its feed-forward (`mlp`, or null for none).  A layer with `weights_of: j` has no tensors
-of its own: it runs layer j's weights on a cache and state of its own.  `vocab`, `width`, `norm.eps`,
-`residual_mult` and `embedding.scale` are the model's own; `max_positions` and `eos_token_id` are optional.  Every size
-and every constant that the file gives is read from it; what the design fixes is stated in `plan()`:
+of its own: it runs layer j's mixer, feed-forward and norms (with j's sizes and constants) on a cache and state of
+its own.  `vocab`, `width`, `norm.eps`, `residual_mult` and `embedding.scale` are the model's own; `max_positions` and
+`eos_token_id` are optional.  Every size and every constant that the file gives is read from it; what the design fixes
+is stated in `plan()`:
 
   * a sublayer reads the residual stream itself and is normed behind: x += residual_mult * norm(sublayer(x));
   * mixer `attention`: grouped-query attention; q, k and v pass a causal convolution over time of `conv` taps right
@@ -209,11 +210,10 @@ class GapevikConfig:
                     raise ConfigError(f"layers[{i}].mlp.router.top {f.top} must lie in 1..{f.experts + f.identity}")
             if L.weights_of is not None:
                 j = L.weights_of
-                if not 0 <= j < i or c.layers[j].weights_of is not None:
-                    raise ConfigError(f"layers[{i}].weights_of {j}: not an earlier layer with weights of its own")
-                o = c.layers[j]
-                if (o.type, o.mixer, o.mlp) != (L.type, L.mixer, L.mlp):
-                    raise ConfigError(f"layers[{i}].weights_of {j}: the two layers' entries differ")
+                if not 0 <= j < len(c.layers) or j == i or c.layers[j].weights_of is not None:
+                    raise ConfigError(f"layers[{i}].weights_of {j}: not another layer with weights of its own")
+                if c.layers[j].type != L.type:
+                    raise ConfigError(f"layers[{i}].weights_of {j}: that layer is a {c.layers[j].type} layer, this one {L.type}")
 
     # ------------------------------------------------------------------ writing
     def to_dict(self) -> dict:

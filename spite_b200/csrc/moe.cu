@@ -265,10 +265,9 @@ __global__ void __launch_bounds__(256) moe_identity_kernel(const T* __restrict__
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
-    float w = 0.f;
     bool any = false;
     for (int s = 0; s < top_k; ++s)
-        if (expert_ids[(size_t)s * n_tokens + t] >= first_identity) { w += weights[(size_t)s * n_tokens + t]; any = true; }
+        if (expert_ids[(size_t)s * n_tokens + t] >= first_identity) any = true;
     if (!any && accumulate) return;
     const T* in = x + (size_t)t * d;
     float* o = out + (size_t)t * d;
@@ -283,7 +282,6 @@ __global__ void __launch_bounds__(256) moe_identity_kernel(const T* __restrict__
         }
         o[c] = accumulate ? o[c] + v : v;
     }
-    (void)w;
 }
 
 }  // namespace

@@ -47,7 +47,7 @@ def test_tensor_names_and_borrowed_layers():
 @pytest.mark.parametrize("change,word", [
     (lambda c: c["layers"][3].update(weights_of=3), "weights_of"),
     (lambda c: c["layers"][5].update(weights_of=3), "weights_of"),
-    (lambda c: c["layers"][3]["mixer"].update(dim=12), "differ"),
+    (lambda c: c["layers"][3].update(type="delta", mixer=c["layers"][2]["mixer"]), "that layer is"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "rot.dims"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=26), "rot.dims"),
     (lambda c: c["layers"][0]["mixer"].update(heads=3), "multiple"),
