@@ -95,9 +95,14 @@ __device__ __forceinline__ float sink_of(const AttentionParams& p, int head) {
 __device__ __forceinline__ float slope_of(const AttentionParams& p, int head) {
     return p.head_slopes ? p.head_slopes[head] : 0.f;
 }
-// A scaled score squashed into (-cap, cap), or itself without a cap.
+// A scaled score squashed into (-cap, cap), or itself without a cap.  The tensor-core kernels are compiled in both
+// forms (CAP): with the choice made per score at run time, the decode kernel took a tenth longer without any cap.
 __device__ __forceinline__ float capped(const AttentionParams& p, float s) {
     return p.score_softcap > 0.f ? p.score_softcap * tanhf(s / p.score_softcap) : s;
+}
+template <bool CAP> __device__ __forceinline__ float capped_if(const AttentionParams& p, float s) {
+    if constexpr (CAP) return p.score_softcap * tanhf(s / p.score_softcap);
+    else return s;
 }
 // The factor on a finished output row.
 __device__ __forceinline__ float gate_of(const AttentionParams& p, int token, int head) {

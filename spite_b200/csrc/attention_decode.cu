@@ -69,7 +69,7 @@ __device__ __forceinline__ unsigned tile_addr(unsigned base, int r, int ch) {
 }
 
 // NKB = head_dim / 64.  grid (blocks over the served segments, kv heads, splits).
-template <int NKB>
+template <int NKB, bool CAP>
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v,
                                                               const AttentionParams p, const StepTokens b,
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
                         for (int e = 0; e < 2; ++e) {
                             const int j = j0 + 8 * n + 2 * cc + e;
                             const bool vis = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                            const float v = vis ? capped(p, sc[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
+                            const float v = vis ? capped_if<CAP>(p, sc[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                             sc[n][2 * h + e] = v;
                             mx = fmaxf(mx, v);
                         }
@@ -431,7 +431,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
     ring = (ring + 15) & ~(size_t)15;
     const size_t smem = ring + sizeof(Tail) + 1024;
     if (smem > 227 * 1024) return SPITE_UNSUPPORTED;
-    auto k = attn_decode_kernel<NKB>;
+    auto k = p.score_softcap > 0.f ? attn_decode_kernel<NKB, true> : attn_decode_kernel<NKB, false>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;

@@ -53,7 +53,7 @@ __device__ __forceinline__ unsigned pack_bf16(float a, float b) {
 }
 
 // NK = head_dim / 16
-template <int NK>
+template <int NK, bool CAP>
 __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionParams p, const StepTokens b,
                                                               const PagedCache c, const AttnMmaExtra x) {
     constexpr int HD = 16 * NK;
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + 8 * n + 2 * cc + e;
                     const bool ok = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                    const float v = ok ? capped(p, s[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
+                    const float v = ok ? capped_if<CAP>(p, s[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                     s[n][2 * h + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -340,7 +340,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
     const size_t tiles = (size_t)WARPS * 4 * TILE * 16 * NK * 2;
     const size_t merge = (size_t)WARPS * 16 * 16 * NK * 4 + WARPS * 16 * 2 * 4;
     const size_t smem = tiles > merge ? tiles : merge;
-    auto k = attn_mma_kernel<NK>;
+    auto k = p.score_softcap > 0.f ? attn_mma_kernel<NK, true> : attn_mma_kernel<NK, false>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;

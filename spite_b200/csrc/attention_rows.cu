@@ -48,7 +48,7 @@ __device__ __forceinline__ unsigned pack_bf16(float a, float b) {
 }
 
 // NK = head_dim / 16
-template <int NK>
+template <int NK, bool CAP>
 __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionParams p, const StepTokens b,
                                                                const PagedCache c, const AttnMmaExtra x) {
     constexpr int HD = 16 * NK;
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
                     for (int e = 0; e < 2; ++e) {
                         const int j = j0 + 8 * n + 2 * cc + e;
                         const bool ok = row_ok[h] && j >= row_lo[h] && j <= row_pos[h];
-                        const float v = ok ? capped(p, s[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
+                        const float v = ok ? capped_if<CAP>(p, s[n][2 * h + e] * p.softmax_scale) - row_slope[h] * (float)(row_pos[h] - j) : -INFINITY;
                         s[n][2 * h + e] = v;
                         mx = fmaxf(mx, v);
                     }
@@ -252,7 +252,7 @@ template <int NK>
 int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, const AttnMmaExtra& x,
            int n_blocks, cudaStream_t st) {
     const size_t smem = (size_t)STAGES * 2 * TILE * 16 * NK * 2;
-    auto k = attn_rows_kernel<NK>;
+    auto k = p.score_softcap > 0.f ? attn_rows_kernel<NK, true> : attn_rows_kernel<NK, false>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;

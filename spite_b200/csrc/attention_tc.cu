@@ -81,7 +81,7 @@ __device__ __forceinline__ unsigned pack_bf16(float a, float b) {
 }
 
 // NKB = head_dim / 64.  grid (blocks over (request, pair of token tiles), kv heads).
-template <int NKB>
+template <int NKB, bool CAP>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const AttentionParams p, const StepTokens b,
@@ -327,7 +327,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     // element with a constant that the compiler knows; the first is the same for the whole tile and joins
                     // the maximum and the exponent's offset below.
                     const float tile_bias = biased ? bias_raw * (float)(j0 - pos) : 0.f;
-                    if (cap_raw > 0.f) {
+                    if constexpr (CAP) {
                         // cap tanh(s scale / cap) in units of the raw scores: tanh(x) = 1 - 2 / (e^(2x) + 1), whose absolute
                         // error (a few float32 roundings of a number below one) times the cap is far below a bfloat16 weight's
 #pragma unroll
@@ -460,7 +460,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
         if (!make_map(&mv, (const __nv_bfloat16*)c.kv + c.v_offset, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
     }
     const size_t smem = 2 * (size_t)NKB * BM * 128 + 2 * ST * (size_t)NKB * BN * 128;
-    auto k = attn_tc_kernel<NKB>;
+    auto k = p.score_softcap > 0.f ? attn_tc_kernel<NKB, true> : attn_tc_kernel<NKB, false>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const long long items = (long long)n_blocks * nkv;

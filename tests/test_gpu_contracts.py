@@ -191,6 +191,67 @@ def test_router_entry_point(libs):
     assert untouched(ids, rows, wts, logits, offs)
 
 
+def test_convolution_cast_identity_and_delta_entry_points(libs):
+    """The entry points of the short convolution, the cast, the identity experts and the delta rule refuse malformed calls
+    and sizes outside their domain, and launch nothing then."""
+    from spite_b200.kernels.cuda import DeltaParams, ShortConvParams
+    ew, moe, delta = libs["elementwise"], libs["moe"], libs["delta"]
+    M, ch, taps = 4, 16, 3
+    x = torch.ones((M, ch + 2), dtype=torch.float32, device=DEV)
+    w = torch.ones((ch, taps), dtype=torch.float32, device=DEV)
+    out, state = canary((M, ch + 2), torch.bfloat16), canary((2, (taps - 1) * ch))
+    cu = torch.tensor([0, 3, 4], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, 0], dtype=torch.int32, device=DEV)
+
+    def conv(dt=1, **kw):
+        a = dict(x=x.data_ptr(), x_stride=ch + 2, w=w.data_ptr(), out=out.data_ptr(), out_stride=ch + 2, state=state.data_ptr(),
+                 slot_stride=(taps - 1) * ch, cu_seqlens=cu.data_ptr(), slots=slots.data_ptr(), n_segments=2, channels=ch, taps=taps,
+                 copy_columns=2, activation=0, max_seg_len=3)
+        a.update(kw)
+        return ew.spite_short_conv(dt, C.byref(ShortConvParams(**a)), None)
+    for kw in (dict(x=None), dict(w=None), dict(out=None), dict(state=None), dict(cu_seqlens=None), dict(slots=None), dict(n_segments=-1),
+               dict(channels=0), dict(taps=0), dict(copy_columns=-1), dict(x_stride=ch), dict(out_stride=ch + 1), dict(slot_stride=ch),
+               dict(activation=2), dict(max_seg_len=-1), dict(dt=7)):
+        assert conv(**kw) == BAD_ARG, kw
+    assert conv(taps=9, slot_stride=8 * ch) == UNSUPPORTED
+    assert ew.spite_short_conv(1, None, None) == BAD_ARG
+    assert untouched(out, state)
+    c = canary((M, ch), torch.bfloat16)
+    for args in ((1, None, ptr(c), C.c_longlong(M * ch)), (1, ptr(x), None, C.c_longlong(M * ch)), (1, ptr(x), ptr(c), C.c_longlong(-1)),
+                 (3, ptr(x), ptr(c), C.c_longlong(M * ch))):
+        assert ew.spite_cast_rows(*args, None) == BAD_ARG, args
+    assert untouched(c)
+    xb = torch.ones((M, ch), dtype=torch.bfloat16, device=DEV)
+    ids, wts, y = torch.zeros((2, M), dtype=torch.int32, device=DEV), torch.ones((2, M), device=DEV), canary((M, ch))
+    for args in ((1, None, ptr(ids), ptr(wts), M, ch, 2, 0, ptr(y), 1), (1, ptr(xb), None, ptr(wts), M, ch, 2, 0, ptr(y), 1),
+                 (1, ptr(xb), ptr(ids), None, M, ch, 2, 0, ptr(y), 1), (1, ptr(xb), ptr(ids), ptr(wts), M, ch, 2, 0, None, 1),
+                 (1, ptr(xb), ptr(ids), ptr(wts), -1, ch, 2, 0, ptr(y), 1), (1, ptr(xb), ptr(ids), ptr(wts), M, 0, 2, 0, ptr(y), 1),
+                 (1, ptr(xb), ptr(ids), ptr(wts), M, ch, 0, 0, ptr(y), 1), (1, ptr(xb), ptr(ids), ptr(wts), M, ch, 2, -1, ptr(y), 1),
+                 (4, ptr(xb), ptr(ids), ptr(wts), M, ch, 2, 0, ptr(y), 1)):
+        assert moe.spite_moe_identity(*args, None) == BAD_ARG, args
+    assert untouched(y)
+    heads, kvh, dim, vdim = 2, 1, 8, 4
+    width = 2 * kvh * dim + heads * vdim + 2 * heads
+    xd = torch.ones((M, width), dtype=torch.float32, device=DEV)
+    a_log, dtb = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV)
+    o, st, gates = canary((M, heads * vdim)), canary((2, heads * dim * vdim)), canary((M, 2 * kvh + 2 * heads))
+
+    def scan(**kw):
+        a = dict(x=xd.data_ptr(), stride=width, q_col=0, k_col=kvh * dim, v_col=2 * kvh * dim, b_col=2 * kvh * dim + heads * vdim,
+                 a_col=2 * kvh * dim + heads * vdim + heads, a_log=a_log.data_ptr(), dt_bias=dtb.data_ptr(), out=o.data_ptr(),
+                 state=st.data_ptr(), slot_stride=heads * dim * vdim, cu_seqlens=cu.data_ptr(), slots=slots.data_ptr(), n_segments=2,
+                 heads=heads, kv_heads=kvh, dim=dim, vdim=vdim, q_scale=1.0, unit_eps=1e-6, gates=gates.data_ptr(), n_tokens=M)
+        a.update(kw)
+        return delta.spite_delta_scan(C.byref(DeltaParams(**a)), 0, None)
+    for kw in (dict(x=None), dict(a_log=None), dict(dt_bias=None), dict(out=None), dict(state=None), dict(cu_seqlens=None), dict(slots=None),
+               dict(gates=None), dict(n_segments=-1), dict(heads=0), dict(kv_heads=0), dict(heads=3, kv_heads=2), dict(dim=0), dict(vdim=0),
+               dict(slot_stride=3), dict(unit_eps=-1.0), dict(q_col=-1), dict(stride=width - 1), dict(n_tokens=-1)):
+        assert scan(**kw) == BAD_ARG, kw
+    assert scan(dim=513, slot_stride=heads * 513 * vdim, stride=4096) == UNSUPPORTED
+    assert delta.spite_delta_scan(None, 0, None) == BAD_ARG
+    assert untouched(o, st, gates)
+
+
 def test_sampling_entry_points(libs):
     from spite_b200.kernels.cuda import SampleParams
     lib = libs["sampling"]
