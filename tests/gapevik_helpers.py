@@ -69,12 +69,12 @@ CONFIG_A = _model(211, 72, 1e-5, 0.5, 3.0, [
 ])
 
 # rows of 64 and 128 elements and a width of 128: the tcgen05 and TMA kernels; a chunk and a window that cross pages;
-# delta heads of 64 x 64 and of 136 x 40; conv of 4 taps
+# six delta heads of 64 x 64 on three q/k heads and two of 136 x 40; conv of 4 taps
 _B1 = _layer("latent_attention", _latent(8, 32, 32, 32, 64, 96, 0.12, 20000.0, window=100), _moe(64, 6, 2, 2))
 CONFIG_B = _model(520, 128, 1e-6, 0.5, 11.3, [
-    _layer("attention", _attn(4, 2, 64, 64, 0.125, 32, 5e5, chunk=150, softcap=30.0, conv=4), _moe(96, 8, 2, 2)),
+    _layer("attention", _attn(4, 2, 64, 64, 0.125, 32, 5e5, chunk=150, softcap=30.0, conv=4), _moe(80, 6, 3, 2)),
     _B1,
-    _layer("delta", _delta(4, 2, 64, 64, 4), _moe(64, 4, 1, 2)),
+    _layer("delta", _delta(6, 3, 64, 64, 4), _moe(64, 4, 1, 2)),
     _layer("latent_attention", _latent(4, 16, 16, 48, 40, 48, 0.15, 1e4, window=64), None),
     dict(_B1, weights_of=1),
     _layer("delta", _delta(2, 2, 136, 40, 4), None),
